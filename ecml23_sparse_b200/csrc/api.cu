@@ -1,0 +1,232 @@
+// extern "C" entry points of include/ffi_b200.h: argument checks, x layout handling,
+// workspace carving and dispatch to the kernel launchers.
+#include <cstring>
+#include <mutex>
+
+#include "ffi_common.cuh"
+
+namespace ffi {
+
+namespace {
+thread_local char g_error[512] = "";
+}
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+int fail(int status, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+int get_device_info(DeviceInfo* info) {
+    static std::mutex mu;
+    static DeviceInfo cache[64];
+    static bool known[64] = {};
+    int dev = 0;
+    FFI_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(FFI_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!known[dev]) {
+        DeviceInfo d;
+        int major = 0;
+        FFI_CUDA_CHECK(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        FFI_CUDA_CHECK(cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        FFI_CUDA_CHECK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        if (major != 10)
+            return fail(FFI_ERR_UNSUPPORTED, "this library is built for sm_100a only (device is sm_%d*)", major * 10);
+        cache[dev] = d;
+        known[dev] = true;
+    }
+    *info = cache[dev];
+    return FFI_OK;
+}
+
+bool forward_uses_smem_x(int B, int N, int K, int* bpl_out);
+bool grad_w_uses_smem_x(int B, int N, int K, int* bpl_out);
+
+namespace {
+
+constexpr size_t kAlign = 256;
+size_t align_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
+
+int check_shape(int64_t B, int64_t N, int64_t L, int64_t K) {
+    if (B <= 0 || N <= 0 || L <= 0 || K <= 0)
+        return fail(FFI_ERR_INVALID_ARGUMENT, "B, N, L, K must be positive (got %lld, %lld, %lld, %lld)",
+                    (long long)B, (long long)N, (long long)L, (long long)K);
+    // Same bound as the reference (tfsparse/cc/kernels/forward.cu:24-28); L*K indexes int32 positions.
+    const int64_t lim = (1LL << 31) - 1;
+    if (B >= lim || N >= lim || L >= lim || K >= lim || L * K >= lim - 1024)
+        return fail(FFI_ERR_UNSUPPORTED, "dimension too large for 32-bit indexing");
+    return FFI_OK;
+}
+
+// How x reaches the kernels: either used in place ([N,B] input, shared-memory path) or
+// copied into the workspace as xT[N][Bpad].
+struct XPlan {
+    bool copy = false;
+    int64_t ld = 0;
+    size_t bytes = 0;
+};
+
+XPlan plan_x(bool smem_path, int64_t B, int64_t N, int x_transposed) {
+    XPlan xp;
+    if (smem_path && x_transposed) {
+        xp.copy = false;
+        xp.ld = B;
+        return xp;
+    }
+    xp.copy = true;
+    xp.ld = round_up(B, 128);
+    xp.bytes = align_up(static_cast<size_t>(N) * xp.ld * 4);
+    return xp;
+}
+
+int stage_x(const XPlan& xp, const float* x, float* ws, int64_t B, int64_t N, int x_transposed,
+            cudaStream_t stream, const float** xT) {
+    if (!xp.copy) {
+        *xT = x;
+        return FFI_OK;
+    }
+    if (x_transposed) {
+        if (xp.ld != B) FFI_CUDA_CHECK(cudaMemsetAsync(ws, 0, static_cast<size_t>(N) * xp.ld * 4, stream));
+        FFI_CUDA_CHECK(cudaMemcpy2DAsync(ws, xp.ld * 4, x, B * 4, B * 4, N, cudaMemcpyDeviceToDevice, stream));
+    } else {
+        int rc = launch_transpose_pad(x, ws, static_cast<int>(B), static_cast<int>(N), xp.ld, stream);
+        if (rc != FFI_OK) return rc;
+    }
+    *xT = ws;
+    return FFI_OK;
+}
+
+}  // namespace
+}  // namespace ffi
+
+using namespace ffi;
+
+extern "C" const char* ffi_last_error(void) { return g_error; }
+
+extern "C" int ffi_version(void) { return 100; }
+
+extern "C" size_t ffi_forward_workspace_bytes(int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed,
+                                              int dtype) {
+    if (check_shape(B, N, L, K) != FFI_OK || dtype != FFI_F32) return 0;
+    const bool smem = forward_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
+    return plan_x(smem, B, N, x_transposed).bytes;
+}
+
+extern "C" int ffi_forward(const void* x, const int32_t* idx, const void* W, const float* bias, float* y,
+                           int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed, int dtype,
+                           void* workspace, size_t workspace_bytes, void* stream_v) {
+    if (!x || !idx || !W || !y) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_forward");
+    int rc = check_shape(B, N, L, K);
+    if (rc != FFI_OK) return rc;
+    if (dtype != FFI_F32) return fail(FFI_ERR_UNSUPPORTED, "ffi_forward: dtype %d not supported", dtype);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+    const bool smem = forward_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
+    const XPlan xp = plan_x(smem, B, N, x_transposed);
+    if (xp.copy && (!workspace || workspace_bytes < xp.bytes || reinterpret_cast<uintptr_t>(workspace) % 16 != 0))
+        return fail(FFI_ERR_WORKSPACE, "ffi_forward needs %zu bytes of 16-byte aligned workspace, got %zu",
+                    xp.bytes, workspace_bytes);
+    const float* xT = nullptr;
+    rc = stage_x(xp, static_cast<const float*>(x), static_cast<float*>(workspace), B, N, x_transposed, stream, &xT);
+    if (rc != FFI_OK) return rc;
+
+    FwdArgs a;
+    a.xT = xT;
+    a.ldx = xp.ld;
+    a.idx = idx;
+    a.W = static_cast<const float*>(W);
+    a.bias = bias;
+    a.y = y;
+    a.B = static_cast<int>(B);
+    a.N = static_cast<int>(N);
+    a.L = static_cast<int>(L);
+    a.K = static_cast<int>(K);
+    return launch_forward(a, stream);
+}
+
+extern "C" size_t ffi_backward_workspace_bytes(const ffi_plan* plan, int64_t B, int64_t N, int64_t L, int64_t K,
+                                               int x_transposed, int dtype, int want_grad_x, int want_grad_w) {
+    if (check_shape(B, N, L, K) != FFI_OK || dtype != FFI_F32) return 0;
+    size_t total = 0;
+    if (want_grad_w) {
+        const bool smem = grad_w_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
+        total += plan_x(smem, B, N, x_transposed).bytes;
+    }
+    if (want_grad_x && plan) total += align_up(grad_x_workspace_bytes(plan, B));
+    return total;
+}
+
+extern "C" int ffi_backward(const void* x, const int32_t* idx, const void* W, const float* g,
+                            const ffi_plan* plan, float* grad_x, float* grad_w, float* grad_bias, int64_t B,
+                            int64_t N, int64_t L, int64_t K, int x_transposed, int dtype, void* workspace,
+                            size_t workspace_bytes, void* stream_v) {
+    if (!x || !idx || !W || !g) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_backward");
+    int rc = check_shape(B, N, L, K);
+    if (rc != FFI_OK) return rc;
+    if (dtype != FFI_F32) return fail(FFI_ERR_UNSUPPORTED, "ffi_backward: dtype %d not supported", dtype);
+    if (grad_x) {
+        if (!plan) return fail(FFI_ERR_INVALID_ARGUMENT, "grad_x needs a plan (ffi_plan_create)");
+        if (plan->L != L || plan->K != K || plan->N != N)
+            return fail(FFI_ERR_STALE_PLAN, "plan was built for (L,K,N)=(%lld,%lld,%lld), call has (%lld,%lld,%lld)",
+                        (long long)plan->L, (long long)plan->K, (long long)plan->N, (long long)L, (long long)K,
+                        (long long)N);
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    size_t used = 0;
+    if (workspace && reinterpret_cast<uintptr_t>(workspace) % kAlign != 0)
+        return fail(FFI_ERR_WORKSPACE, "workspace must be %zu-byte aligned", kAlign);
+
+    if (grad_w || grad_bias) {
+        const bool smem = grad_w_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
+        const XPlan xp = plan_x(smem, B, N, x_transposed);
+        if (xp.copy && (!workspace || workspace_bytes < used + xp.bytes))
+            return fail(FFI_ERR_WORKSPACE, "ffi_backward needs %zu more bytes of workspace for x", xp.bytes);
+        const float* xT = nullptr;
+        rc = stage_x(xp, static_cast<const float*>(x), reinterpret_cast<float*>(ws + used), B, N, x_transposed,
+                     stream, &xT);
+        if (rc != FFI_OK) return rc;
+        used += xp.bytes;
+        GradWArgs a;
+        a.xT = xT;
+        a.ldx = xp.ld;
+        a.idx = idx;
+        a.g = g;
+        a.gW = grad_w;
+        a.gbias = grad_bias;
+        a.B = static_cast<int>(B);
+        a.N = static_cast<int>(N);
+        a.L = static_cast<int>(L);
+        a.K = static_cast<int>(K);
+        rc = launch_grad_w(a, stream);
+        if (rc != FFI_OK) return rc;
+    }
+    if (grad_x) {
+        GradXArgs a;
+        a.idx = idx;
+        a.W = static_cast<const float*>(W);
+        a.g = g;
+        a.plan = plan;
+        a.gx = grad_x;
+        a.x_transposed = x_transposed;
+        a.B = static_cast<int>(B);
+        a.N = static_cast<int>(N);
+        a.L = static_cast<int>(L);
+        a.K = static_cast<int>(K);
+        a.workspace = workspace ? ws + used : nullptr;
+        a.workspace_bytes = workspace_bytes > used ? workspace_bytes - used : 0;
+        rc = launch_grad_x(a, stream);
+        if (rc != FFI_OK) return rc;
+    }
+    return FFI_OK;
+}

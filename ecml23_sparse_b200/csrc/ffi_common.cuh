@@ -1,0 +1,128 @@
+// Internal helpers shared by the kernels behind include/ffi_b200.h (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_pipeline.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "ffi_b200.h"
+
+namespace ffi {
+
+// ---- error reporting ------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int fail(int status, const char* fmt, ...);
+
+#define FFI_CUDA_CHECK(expr)                                                               \
+    do {                                                                                   \
+        cudaError_t _e = (expr);                                                           \
+        if (_e != cudaSuccess)                                                             \
+            return ::ffi::fail(FFI_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,               \
+                               cudaGetErrorString(_e), __FILE__, __LINE__);                \
+    } while (0)
+
+#define FFI_LAUNCH_CHECK(name)                                                             \
+    do {                                                                                   \
+        cudaError_t _e = cudaGetLastError();                                               \
+        if (_e != cudaSuccess)                                                             \
+            return ::ffi::fail(FFI_ERR_CUDA, "launch of %s failed: %s", name,              \
+                               cudaGetErrorString(_e));                                    \
+    } while (0)
+
+// ---- device properties (cached per device) ---------------------------------------
+struct DeviceInfo {
+    int sm_count = 0;
+    int max_smem_optin = 0;  // bytes of dynamic shared memory one CTA may opt in to
+};
+int get_device_info(DeviceInfo* info);
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+
+// ---- vector of BPL batch elements held by one lane --------------------------------
+template <int BPL>
+struct Vec;
+template <>
+struct Vec<1> {
+    using type = float;
+};
+template <>
+struct Vec<2> {
+    using type = float2;
+};
+template <>
+struct Vec<4> {
+    using type = float4;
+};
+
+__device__ __forceinline__ float vec_get(const float& v, int) { return v; }
+__device__ __forceinline__ float vec_get(const float2& v, int j) { return j == 0 ? v.x : v.y; }
+__device__ __forceinline__ float vec_get(const float4& v, int j) {
+    return j == 0 ? v.x : (j == 1 ? v.y : (j == 2 ? v.z : v.w));
+}
+
+// ---- launchers implemented in the .cu files ---------------------------------------
+// xT is x in [N][ldx] layout (batch contiguous), fp32.
+struct FwdArgs {
+    const float* xT;
+    int64_t ldx;
+    const int32_t* idx;
+    const float* W;
+    const float* bias;
+    float* y;
+    int B, N, L, K;
+};
+int launch_forward(const FwdArgs& a, cudaStream_t stream);
+
+struct GradWArgs {
+    const float* xT;
+    int64_t ldx;
+    const int32_t* idx;
+    const float* g;
+    float* gW;
+    float* gbias;
+    int B, N, L, K;
+};
+int launch_grad_w(const GradWArgs& a, cudaStream_t stream);
+
+// x [B,N] -> xT [N][ldx] (zero padded to ldx), fp32.
+int launch_transpose_pad(const float* src, float* dst, int rows, int cols, int64_t ld_dst,
+                         cudaStream_t stream);
+
+}  // namespace ffi
+
+// The plan object (defined in plan.cu, used by backward.cu and api.cu).
+struct ffi_plan {
+    int64_t L = 0, K = 0, N = 0;
+    int device = 0;
+    int chunk_rows = 0;     // T: outputs per chunk of the chunked lists
+    int64_t n_chunks = 0;   // ceil(L / T)
+    bool has_chunks = false;
+    int32_t* rowptr = nullptr;  // [N+1]   canonical CSR-by-input
+    int32_t* perm = nullptr;    // [L*K]   positions sorted by (idx[p], p)
+    int32_t* cperm = nullptr;   // [L*K]   chunk-major: chunk c holds its T*K positions sorted by (idx[p], p)
+    int32_t* cptr = nullptr;    // [n_chunks][N+1] offsets of each input's run inside its chunk
+    size_t device_bytes = 0;
+};
+
+namespace ffi {
+
+struct GradXArgs {
+    const int32_t* idx;
+    const float* W;
+    const float* g;
+    const ffi_plan* plan;
+    float* gx;
+    int x_transposed;  // layout of gx: [N,B] if set, else [B,N]
+    int B, N, L, K;
+    void* workspace;
+    size_t workspace_bytes;
+};
+size_t grad_x_workspace_bytes(const ffi_plan* plan, int64_t B);
+int launch_grad_x(const GradXArgs& a, cudaStream_t stream);
+
+}  // namespace ffi

@@ -1,0 +1,298 @@
+// Forward of the fixed-fan-in sparse layer on sm_100a:
+//   y[b,o] = bias[o] + sum_k W[o,k] * x[b, idx[o,k]]
+//
+// Replaces the reference's forward kernels (tfsparse/cc/kernels/forward.cu.h:231-264:
+// forward_ob_scalar_tp for the transposed op, forward_ib_unrolled for the plain one),
+// their output memset (forward.cu:63) and the separate bias_add (sparse/layer.py:247).
+//
+// Dataflow.  One lane owns BPL batch elements (a warp covers BT = 32*BPL of them) and a
+// warp walks whole output rows, so (o,k) is warp-uniform:
+//   * the batch tile of x sits in shared memory as x_s[N][BT] (batch contiguous), so the
+//     gather x[:, idx[o,k]] is one conflict-free 4/8/16-byte LDS per lane;
+//   * W and idx rows stream through a double-buffered shared-memory tile filled with
+//     cp.async (no register staging) and are read back as 16-byte broadcasts;
+//   * results go through a padded shared-memory tile so that the global stores of y run
+//     along o (128 B per warp store) instead of striding by L.
+// The kernel is persistent: gridDim.x CTAs per batch tile loop over the output tiles.
+// When x_s does not fit (wide N), the same code gathers x from global memory (L2).
+#include "ffi_common.cuh"
+
+namespace ffi {
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kWarps = kThreads / 32;
+
+struct FwdKernelParams {
+    const float* xT;
+    long long ldx;
+    const int* idx;
+    const float* W;
+    const float* bias;
+    float* y;
+    int B, N, L, K;
+    int Kp;        // K rounded up to a multiple of 4 (row stride of the staged tiles)
+    int TO;        // outputs per tile
+    int numTiles;  // ceil(L / TO)
+    int vec16;     // tiles can be copied with 16-byte cp.async
+};
+
+template <int BPL, bool XSMEM>
+__global__ void __launch_bounds__(kThreads, 1) ffi_fwd_kernel(FwdKernelParams p) {
+    constexpr int BT = 32 * BPL;
+    using V = typename Vec<BPL>::type;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+
+    float* x_s = reinterpret_cast<float*>(smem_raw);
+    float* w_s = x_s + (XSMEM ? static_cast<size_t>(p.N) * BT : 0);
+    int* i_s = reinterpret_cast<int*>(w_s + 2 * p.TO * p.Kp);
+    float* y_s = reinterpret_cast<float*>(i_s + 2 * p.TO * p.Kp);
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int b0 = blockIdx.y * BT;
+    const int TO = p.TO, Kp = p.Kp, K = p.K, L = p.L;
+    const int tileElems = TO * Kp;
+
+    // Padding slots (k in [K,Kp)) and rows never copied must hold weight 0 / index 0.
+    for (int e = tid; e < 2 * tileElems; e += kThreads) {
+        w_s[e] = 0.f;
+        i_s[e] = 0;
+    }
+    if (XSMEM) {
+        // x_s[i][lane*BPL + j] holds batch element b0 + lane + 32*j.
+        const int total = p.N * BT;
+        for (int e = tid; e < total; e += kThreads) {
+            int i = e / BT;
+            int bl = e - i * BT;
+            int b = b0 + bl;
+            float v = b < p.B ? p.xT[static_cast<size_t>(i) * p.ldx + b] : 0.f;
+            x_s[i * BT + (bl & 31) * BPL + (bl >> 5)] = v;
+        }
+    }
+    __syncthreads();
+
+    auto prefetch = [&](int t, int buf) {
+        const long long o0 = static_cast<long long>(t) * TO;
+        const int nrows = min(TO, static_cast<int>(L - o0));
+        float* wd = w_s + buf * tileElems;
+        int* id = i_s + buf * tileElems;
+        const float* wsrc = p.W + o0 * K;
+        const int* isrc = p.idx + o0 * K;
+        if (p.vec16) {
+            const int nvec = nrows * K / 4;
+            for (int v = tid; v < nvec; v += kThreads) {
+                __pipeline_memcpy_async(wd + 4 * v, wsrc + 4 * v, 16);
+                __pipeline_memcpy_async(id + 4 * v, isrc + 4 * v, 16);
+            }
+        } else {
+            const int n = nrows * K;
+            for (int e = tid; e < n; e += kThreads) {
+                int r = e / K;
+                int k = e - r * K;
+                __pipeline_memcpy_async(wd + r * Kp + k, wsrc + e, 4);
+                __pipeline_memcpy_async(id + r * Kp + k, isrc + e, 4);
+            }
+        }
+        __pipeline_commit();
+    };
+
+    const V* xs_lane = reinterpret_cast<const V*>(x_s) + lane;
+    const V* xg_lane = reinterpret_cast<const V*>(p.xT + b0) + lane;
+    const size_t ldv = static_cast<size_t>(p.ldx / BPL);
+
+    int t = blockIdx.x;
+    int buf = 0;
+    if (t < p.numTiles) prefetch(t, 0);
+    for (; t < p.numTiles; t += gridDim.x, buf ^= 1) {
+        __pipeline_wait_prior(0);
+        __syncthreads();  // tile t landed; y_s and the other tile buffer are free again
+        const int tn = t + gridDim.x;
+        if (tn < p.numTiles) prefetch(tn, buf ^ 1);
+
+        const long long o0 = static_cast<long long>(t) * TO;
+        const float* wb = w_s + buf * tileElems;
+        const int* ib = i_s + buf * tileElems;
+        for (int ol = warp; ol < TO; ol += kWarps) {
+            const long long o = o0 + ol;
+            if (o >= L) break;
+            const float bias = p.bias ? __ldg(p.bias + o) : 0.f;
+            float acc[BPL];
+#pragma unroll
+            for (int j = 0; j < BPL; ++j) acc[j] = bias;
+            const int4* ir = reinterpret_cast<const int4*>(ib + ol * Kp);
+            const float4* wr = reinterpret_cast<const float4*>(wb + ol * Kp);
+#pragma unroll 2
+            for (int k4 = 0; k4 < Kp / 4; ++k4) {
+                const int4 ii = ir[k4];
+                const float4 ww = wr[k4];
+                V v0, v1, v2, v3;
+                if (XSMEM) {
+                    v0 = xs_lane[ii.x * 32];
+                    v1 = xs_lane[ii.y * 32];
+                    v2 = xs_lane[ii.z * 32];
+                    v3 = xs_lane[ii.w * 32];
+                } else {
+                    v0 = __ldg(xg_lane + ii.x * ldv);
+                    v1 = __ldg(xg_lane + ii.y * ldv);
+                    v2 = __ldg(xg_lane + ii.z * ldv);
+                    v3 = __ldg(xg_lane + ii.w * ldv);
+                }
+#pragma unroll
+                for (int j = 0; j < BPL; ++j) {
+                    acc[j] = fmaf(ww.x, vec_get(v0, j), acc[j]);
+                    acc[j] = fmaf(ww.y, vec_get(v1, j), acc[j]);
+                    acc[j] = fmaf(ww.z, vec_get(v2, j), acc[j]);
+                    acc[j] = fmaf(ww.w, vec_get(v3, j), acc[j]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < BPL; ++j) {
+                const int bl = XSMEM ? lane + 32 * j : lane * BPL + j;
+                y_s[ol * (BT + 1) + bl] = acc[j];
+            }
+        }
+        __syncthreads();  // y_s complete
+
+        // Coalesced write-out: one warp per batch row, lanes along o.
+        for (int r = warp; r < BT; r += kWarps) {
+            const int b = b0 + r;
+            if (b >= p.B) break;
+            float* yrow = p.y + static_cast<size_t>(b) * L + o0;
+            for (int c = lane; c < TO; c += 32)
+                if (o0 + c < L) yrow[c] = y_s[c * (BT + 1) + r];
+        }
+    }
+    __pipeline_wait_prior(0);
+}
+
+__global__ void transpose_pad_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                     int rows, int cols, long long ld_dst) {
+    // src [rows][cols] -> dst [cols][ld_dst], dst[c][r] = src[r][c]; r in [rows, ld_dst) zero.
+    __shared__ float tile[32][33];
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int dy = threadIdx.y; dy < 32; dy += blockDim.y) {
+        int r = r0 + dy, c = c0 + threadIdx.x;
+        tile[dy][threadIdx.x] = (r < rows && c < cols) ? src[static_cast<size_t>(r) * cols + c] : 0.f;
+    }
+    __syncthreads();
+    for (int dy = threadIdx.y; dy < 32; dy += blockDim.y) {
+        int c = c0 + dy, r = r0 + threadIdx.x;
+        if (c < cols && r < ld_dst) dst[static_cast<size_t>(c) * ld_dst + r] = tile[threadIdx.x][dy];
+    }
+}
+
+struct FwdConfig {
+    int bpl;
+    bool xsmem;
+    int TO;
+    size_t smem;
+};
+
+size_t fwd_smem_bytes(int N, int bpl, bool xsmem, int TO, int Kp) {
+    const size_t BT = 32 * bpl;
+    return (xsmem ? static_cast<size_t>(N) * BT * 4 : 0) + static_cast<size_t>(2) * TO * Kp * 8 +
+           static_cast<size_t>(TO) * (BT + 1) * 4;
+}
+
+int pick_TO(size_t budget, int N, int bpl, bool xsmem, int Kp) {
+    const size_t BT = 32 * bpl;
+    const size_t fixed = xsmem ? static_cast<size_t>(N) * BT * 4 : 0;
+    if (fixed >= budget) return 0;
+    const size_t per_row = static_cast<size_t>(2) * Kp * 8 + (BT + 1) * 4;
+    size_t to = (budget - fixed) / per_row;
+    if (to > 128) to = 128;
+    return static_cast<int>(to / 16 * 16);
+}
+
+template <int BPL, bool XSMEM>
+int launch_fwd_t(const FwdKernelParams& p, size_t smem, int nBT, const DeviceInfo& dev,
+                 cudaStream_t stream) {
+    auto kern = ffi_fwd_kernel<BPL, XSMEM>;
+    FFI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(smem)));
+    int occ = 0;
+    FFI_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kThreads, smem));
+    if (occ < 1) return fail(FFI_ERR_CUDA, "forward kernel does not fit on an SM (smem %zu)", smem);
+    int per_bt = dev.sm_count * occ / nBT;
+    if (per_bt < 1) per_bt = 1;
+    dim3 grid(static_cast<unsigned>(min(p.numTiles, per_bt)), static_cast<unsigned>(nBT));
+    kern<<<grid, kThreads, smem, stream>>>(p);
+    FFI_LAUNCH_CHECK("ffi_fwd_kernel");
+    return FFI_OK;
+}
+
+}  // namespace
+
+// Chooses batch elements per lane and whether the x tile is shared-memory resident.
+// Exposed so that the host wrapper can tell which x layout / padding the launch needs.
+bool forward_uses_smem_x(int B, int N, int K, int* bpl_out) {
+    DeviceInfo dev;
+    if (get_device_info(&dev) != FFI_OK) return false;
+    const int Kp = static_cast<int>(round_up(K, 4));
+    int bpl = B <= 32 ? 1 : (B <= 64 ? 2 : 4);
+    for (int c = bpl; c >= 1; c /= 2) {
+        if (pick_TO(dev.max_smem_optin, N, c, true, Kp) >= 16) {
+            if (bpl_out) *bpl_out = c;
+            return true;
+        }
+    }
+    if (bpl_out) *bpl_out = bpl;
+    return false;
+}
+
+int launch_forward(const FwdArgs& a, cudaStream_t stream) {
+    DeviceInfo dev;
+    int rc = get_device_info(&dev);
+    if (rc != FFI_OK) return rc;
+
+    FwdKernelParams p;
+    p.xT = a.xT;
+    p.ldx = a.ldx;
+    p.idx = a.idx;
+    p.W = a.W;
+    p.bias = a.bias;
+    p.y = a.y;
+    p.B = a.B;
+    p.N = a.N;
+    p.L = a.L;
+    p.K = a.K;
+    p.Kp = static_cast<int>(round_up(a.K, 4));
+    p.vec16 = (a.K % 4 == 0) && (reinterpret_cast<uintptr_t>(a.W) % 16 == 0) &&
+              (reinterpret_cast<uintptr_t>(a.idx) % 16 == 0);
+
+    int bpl = 1;
+    const bool xsmem = forward_uses_smem_x(a.B, a.N, a.K, &bpl);
+    p.TO = pick_TO(dev.max_smem_optin, a.N, bpl, xsmem, p.Kp);
+    if (p.TO < 16) return fail(FFI_ERR_UNSUPPORTED, "fan-in K=%d too large for the staged tiles", a.K);
+    p.numTiles = static_cast<int>(ceil_div(a.L, p.TO));
+    const size_t smem = fwd_smem_bytes(a.N, bpl, xsmem, p.TO, p.Kp);
+    const int nBT = static_cast<int>(ceil_div(a.B, 32 * bpl));
+    if (!xsmem) {
+        // The global-memory gather reads whole lane vectors: rows must be padded and aligned.
+        if (a.ldx % (32 * bpl) != 0 || a.ldx < static_cast<int64_t>(nBT) * 32 * bpl ||
+            reinterpret_cast<uintptr_t>(a.xT) % 16 != 0)
+            return fail(FFI_ERR_INVALID_ARGUMENT, "wide-N forward needs a padded, aligned x copy");
+    }
+
+    if (xsmem) {
+        if (bpl == 4) return launch_fwd_t<4, true>(p, smem, nBT, dev, stream);
+        if (bpl == 2) return launch_fwd_t<2, true>(p, smem, nBT, dev, stream);
+        return launch_fwd_t<1, true>(p, smem, nBT, dev, stream);
+    }
+    if (bpl == 4) return launch_fwd_t<4, false>(p, smem, nBT, dev, stream);
+    if (bpl == 2) return launch_fwd_t<2, false>(p, smem, nBT, dev, stream);
+    return launch_fwd_t<1, false>(p, smem, nBT, dev, stream);
+}
+
+int launch_transpose_pad(const float* src, float* dst, int rows, int cols, int64_t ld_dst,
+                         cudaStream_t stream) {
+    dim3 block(32, 8);
+    dim3 grid(static_cast<unsigned>(ceil_div(cols, 32)), static_cast<unsigned>(ceil_div(ld_dst, 32)));
+    transpose_pad_kernel<<<grid, block, 0, stream>>>(src, dst, rows, cols, ld_dst);
+    FFI_LAUNCH_CHECK("transpose_pad_kernel");
+    return FFI_OK;
+}
+
+}  // namespace ffi

@@ -1,0 +1,377 @@
+// grad_x of the fixed-fan-in sparse layer on sm_100a, deterministic and atomic-free:
+//   grad_x[b,i] = sum over (o,k) with idx[o,k]==i of W[o,k] * g[b,o]
+//
+// Replaces the reference's atomicAdd kernels backward_features_vector(_tp) / _scalar(_tp)
+// and the memset before them (tfsparse/cc/kernels/backward.cu.h:107-185,
+// backward.cu:96,121).  Both paths walk the transposed index of ffi_plan.
+//
+// Narrow inputs (N <= 2048): register-accumulator kernel.  The outputs are cut into the
+// plan's chunks of T rows.  A CTA owns a contiguous range of chunks, a slice of 16*NI
+// inputs and a tile of BT = 32*BPL batch elements; warp w owns NI inputs and keeps their
+// NI x BPL partial sums in registers for the whole range.  Per chunk the CTA
+//   1. copies g[b-tile, chunk] into shared memory transposed (g_s[o][b], 16-byte
+//      granules XOR-swizzled by o so that both the 4-byte cp.async fill and the
+//      per-entry vector gather are bank-conflict free),
+//   2. stages its slice of the chunk's sorted entries as (W[p], row) pairs,
+//   3. lets every warp walk the runs of its inputs: one broadcast LDS per two entries,
+//      one gathered LDS.32/64/128 and BPL FMAs per entry.
+// Range partials go to a workspace and a second kernel adds them in range order, so the
+// summation order is a pure function of (idx, shape): results are bit-reproducible.
+//
+// Wide inputs: g is transposed once into gT[L][Bpad] (workspace) and one warp per
+// (input, batch tile) walks the canonical row, gathering 128 contiguous batch values
+// per entry.
+#include "ffi_common.cuh"
+
+namespace ffi {
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kWarps = kThreads / 32;
+
+struct GxNarrowParams {
+    const float* W;
+    const float* g;
+    const int* cperm;
+    const int* cptr;
+    float* partial;  // [R][N][Bpad]
+    int B, N, L, K;
+    int T;           // rows per chunk
+    long long nChunks;
+    int R;           // number of chunk ranges (gridDim.x)
+    int Bpad;
+    int entCap;      // capacity of the staged entry buffer (entries)
+};
+
+template <int NI, int BPL>
+__global__ void __launch_bounds__(kThreads, 1) ffi_grad_x_narrow_kernel(GxNarrowParams p) {
+    constexpr int BT = 32 * BPL;
+    constexpr int GR = BPL;  // floats per granule
+    constexpr int SW = 32 / GR - 1;  // swizzle mask: rows copied by one warp get distinct granules
+    using V = typename Vec<BPL>::type;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+
+    float* g_s = reinterpret_cast<float*>(smem_raw);                        // [T][BT], swizzled granules
+    uint2* ent_s = reinterpret_cast<uint2*>(g_s + static_cast<size_t>(p.T) * BT);  // (W bits, row)
+    int* cp_s = reinterpret_cast<int*>(ent_s + p.entCap);                   // [16*NI + 1]
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int r = blockIdx.x;
+    const int i_lo = blockIdx.y * (kWarps * NI);
+    const int i_hi = min(p.N, i_lo + kWarps * NI);
+    const int b0 = blockIdx.z * BT;
+    const int T = p.T, K = p.K, L = p.L, N = p.N;
+    const long long c_begin = p.nChunks * r / p.R;
+    const long long c_end = p.nChunks * (r + 1) / p.R;
+
+    float acc[NI][BPL];
+#pragma unroll
+    for (int j = 0; j < NI; ++j)
+#pragma unroll
+        for (int q = 0; q < BPL; ++q) acc[j][q] = 0.f;
+
+    for (long long c = c_begin; c < c_end; ++c) {
+        const long long o0 = c * T;
+        const int nrows = static_cast<int>(min(static_cast<long long>(T), static_cast<long long>(L) - o0));
+        __syncthreads();  // the previous chunk's g_s / ent_s / cp_s are no longer read
+
+        // (1) g tile.  Work item u = (row group of 8, granule, slot, row in group): a warp
+        // covers 8 consecutive rows x BPL slots of one granule -> 32 distinct banks.
+        {
+            constexpr int ROWS_PER_WARP_ITEM = 32 / GR;  // rows covered by one warp-wide copy
+            const int itemsPerGranule = (T + ROWS_PER_WARP_ITEM - 1) / ROWS_PER_WARP_ITEM;
+            const int totalItems = itemsPerGranule * 32;  // x 32 granules
+            for (int it = warp; it < totalItems; it += kWarps) {
+                const int gl = it & 31;                    // logical granule (= lane that will read it)
+                const int rg = it >> 5;                    // row group
+                const int ol = rg * ROWS_PER_WARP_ITEM + lane / GR;
+                const int q = lane % GR;                   // slot inside the granule
+                const int b = b0 + gl * GR + q;
+                if (ol < T) {
+                    float* dst = g_s + static_cast<size_t>(ol) * BT + ((gl ^ (ol & SW)) * GR) + q;
+                    if (ol < nrows && b < p.B)
+                        __pipeline_memcpy_async(dst, p.g + static_cast<size_t>(b) * L + o0 + ol, 4);
+                    else
+                        *dst = 0.f;
+                }
+            }
+            __pipeline_commit();
+        }
+
+        // (2) run offsets of my input slice and the staged entries.
+        const int* cptr_c = p.cptr + c * (N + 1);
+        const int e_lo = __ldg(cptr_c + i_lo);
+        const int e_hi = __ldg(cptr_c + i_hi);
+        for (int t = tid; t <= kWarps * NI; t += kThreads) {
+            const int i = min(i_lo + t, i_hi);
+            cp_s[t] = __ldg(cptr_c + i) - e_lo;
+        }
+        const int* cperm_c = p.cperm + c * static_cast<long long>(T) * K;
+        for (int ebase = 0; ebase < e_hi - e_lo; ebase += p.entCap) {
+            // The slice normally fits entCap at once; an adversarial idx (everything in
+            // one slice) is handled in several rounds.
+            const int cnt = min(p.entCap, e_hi - e_lo - ebase);
+            if (ebase > 0) __syncthreads();
+            for (int e = tid; e < cnt; e += kThreads) {
+                const int pos = __ldg(cperm_c + e_lo + ebase + e);
+                const int ol = pos / K - static_cast<int>(o0);
+                ent_s[e] = make_uint2(__float_as_uint(__ldg(p.W + pos)), static_cast<unsigned>(ol));
+            }
+            __pipeline_wait_prior(0);
+            __syncthreads();
+
+            // (3) walk the runs.
+            const V* gs_v = reinterpret_cast<const V*>(g_s);
+#pragma unroll
+            for (int j = 0; j < NI; ++j) {
+                int s = cp_s[warp * NI + j] - ebase;
+                int t = cp_s[warp * NI + j + 1] - ebase;
+                s = max(s, 0);
+                t = min(t, cnt);
+                int e = s;
+                if ((e & 1) && e < t) {
+                    const uint2 en = ent_s[e];
+                    const int ol = static_cast<int>(en.y);
+                    const V v = gs_v[ol * 32 + (lane ^ (ol & SW))];
+                    const float w = __uint_as_float(en.x);
+#pragma unroll
+                    for (int q = 0; q < BPL; ++q) acc[j][q] = fmaf(w, vec_get(v, q), acc[j][q]);
+                    ++e;
+                }
+                for (; e + 2 <= t; e += 2) {
+                    const uint4 en = *reinterpret_cast<const uint4*>(ent_s + e);
+                    const int ol0 = static_cast<int>(en.y), ol1 = static_cast<int>(en.w);
+                    const V v0 = gs_v[ol0 * 32 + (lane ^ (ol0 & SW))];
+                    const V v1 = gs_v[ol1 * 32 + (lane ^ (ol1 & SW))];
+                    const float w0 = __uint_as_float(en.x), w1 = __uint_as_float(en.z);
+#pragma unroll
+                    for (int q = 0; q < BPL; ++q) {
+                        acc[j][q] = fmaf(w0, vec_get(v0, q), acc[j][q]);
+                        acc[j][q] = fmaf(w1, vec_get(v1, q), acc[j][q]);
+                    }
+                }
+                if (e < t) {
+                    const uint2 en = ent_s[e];
+                    const int ol = static_cast<int>(en.y);
+                    const V v = gs_v[ol * 32 + (lane ^ (ol & SW))];
+                    const float w = __uint_as_float(en.x);
+#pragma unroll
+                    for (int q = 0; q < BPL; ++q) acc[j][q] = fmaf(w, vec_get(v, q), acc[j][q]);
+                }
+            }
+        }
+        if (e_hi == e_lo) {
+            __pipeline_wait_prior(0);
+        }
+    }
+    __pipeline_wait_prior(0);
+
+    // Range partials: partial[r][i][b0 + lane*BPL + q].
+#pragma unroll
+    for (int j = 0; j < NI; ++j) {
+        const int i = i_lo + warp * NI + j;
+        if (i < N) {
+            float* dst = p.partial + (static_cast<size_t>(r) * N + i) * p.Bpad + b0 + lane * BPL;
+#pragma unroll
+            for (int q = 0; q < BPL; ++q) dst[q] = acc[j][q];
+        }
+    }
+}
+
+// gx = sum over ranges of partial[r][i][b], in range order; writes [B,N] or [N,B].
+__global__ void reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ gx,
+                                       int R, int N, int B, int Bpad, int x_transposed) {
+    const long long id = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (id >= static_cast<long long>(N) * Bpad) return;
+    const int i = static_cast<int>(id / Bpad);
+    const int b = static_cast<int>(id - static_cast<long long>(i) * Bpad);
+    if (b >= B) return;
+    double acc = 0.0;  // the range partials are large next to a small total: add them in fp64
+    for (int r = 0; r < R; ++r) acc += static_cast<double>(partial[(static_cast<size_t>(r) * N + i) * Bpad + b]);
+    const float s = static_cast<float>(acc);
+    if (x_transposed) gx[static_cast<size_t>(i) * B + b] = s;
+    else gx[static_cast<size_t>(b) * N + i] = s;
+}
+
+// ---- wide inputs -------------------------------------------------------------------
+
+// One warp per (input i, batch tile of 128): walks row i of the canonical index.
+__global__ void __launch_bounds__(256) ffi_grad_x_wide_kernel(const float* __restrict__ W,
+                                                              const float* __restrict__ gT,
+                                                              const int* __restrict__ rowptr,
+                                                              const int* __restrict__ perm,
+                                                              float* __restrict__ gx, int B, int N,
+                                                              int K, int Bpad, int x_transposed) {
+    const int lane = threadIdx.x & 31;
+    const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int nBT = Bpad / 128;
+    if (wid >= static_cast<long long>(N) * nBT) return;
+    const int i = static_cast<int>(wid / nBT);
+    const int bt = static_cast<int>(wid - static_cast<long long>(i) * nBT);
+    const float4* gT4 = reinterpret_cast<const float4*>(gT + bt * 128) + lane;
+    const size_t ld4 = Bpad / 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int s = rowptr[i], t = rowptr[i + 1];
+    for (int base = s; base < t; base += 32) {
+        const int e = base + lane;
+        int o = 0;
+        float w = 0.f;
+        if (e < t) {
+            const int pos = __ldg(perm + e);
+            o = pos / K;
+            w = __ldg(W + pos);
+        }
+        const int cnt = min(32, t - base);
+        for (int u = 0; u < cnt; ++u) {
+            const int ou = __shfl_sync(0xffffffffu, o, u);
+            const float wu = __shfl_sync(0xffffffffu, w, u);
+            const float4 v = __ldg(gT4 + static_cast<size_t>(ou) * ld4);
+            acc.x = fmaf(wu, v.x, acc.x);
+            acc.y = fmaf(wu, v.y, acc.y);
+            acc.z = fmaf(wu, v.z, acc.z);
+            acc.w = fmaf(wu, v.w, acc.w);
+        }
+    }
+    const int b = bt * 128 + lane * 4;
+    const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        if (b + q < B) {
+            if (x_transposed) gx[static_cast<size_t>(i) * B + b + q] = vals[q];
+            else gx[static_cast<size_t>(b + q) * N + i] = vals[q];
+        }
+    }
+}
+
+template <int NI, int BPL>
+int launch_narrow_t(const GxNarrowParams& p, size_t smem, int iparts, int nBT, cudaStream_t stream) {
+    auto kern = ffi_grad_x_narrow_kernel<NI, BPL>;
+    FFI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(smem)));
+    dim3 grid(static_cast<unsigned>(p.R), static_cast<unsigned>(iparts), static_cast<unsigned>(nBT));
+    kern<<<grid, kThreads, smem, stream>>>(p);
+    FFI_LAUNCH_CHECK("ffi_grad_x_narrow_kernel");
+    return FFI_OK;
+}
+
+struct NarrowConfig {
+    int bpl, ni, iparts, nBT, Bpad, R, entCap;
+    size_t smem;
+};
+
+bool narrow_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, NarrowConfig* c) {
+    if (!plan->has_chunks) return false;
+    c->bpl = B <= 32 ? 1 : (B <= 64 ? 2 : 4);
+    c->ni = 64 / c->bpl;  // 64 accumulator registers per lane
+    const int BT = 32 * c->bpl;
+    c->iparts = static_cast<int>(ceil_div(plan->N, kWarps * c->ni));
+    c->nBT = static_cast<int>(ceil_div(B, BT));
+    c->Bpad = c->nBT * BT;
+    int R = dev.sm_count / (c->iparts * c->nBT);
+    if (R < 1) R = 1;
+    if (R > plan->n_chunks) R = static_cast<int>(plan->n_chunks);
+    c->R = R;
+    const size_t gbytes = static_cast<size_t>(plan->chunk_rows) * BT * 4;
+    const size_t cpbytes = (kWarps * c->ni + 1) * 4 + 16;
+    if (gbytes + cpbytes + 1024 > static_cast<size_t>(dev.max_smem_optin)) return false;
+    size_t cap = (dev.max_smem_optin - gbytes - cpbytes) / 8;
+    const size_t full = static_cast<size_t>(plan->chunk_rows) * plan->K;
+    if (cap > full) cap = full;
+    cap = cap / 2 * 2;
+    if (cap < 64) return false;
+    c->entCap = static_cast<int>(cap);
+    c->smem = gbytes + cap * 8 + cpbytes;
+    return true;
+}
+
+__global__ void transpose_g_kernel(const float* __restrict__ g, float* __restrict__ gT, int B,
+                                   long long L, int Bpad) {
+    // g [B][L] -> gT [L][Bpad] (zero padded batch)
+    __shared__ float tile[32][33];
+    const long long o0 = static_cast<long long>(blockIdx.x) * 32;
+    const int b0 = blockIdx.y * 32;
+    for (int dy = threadIdx.y; dy < 32; dy += blockDim.y) {
+        const int b = b0 + dy;
+        const long long o = o0 + threadIdx.x;
+        tile[dy][threadIdx.x] = (b < B && o < L) ? g[static_cast<size_t>(b) * L + o] : 0.f;
+    }
+    __syncthreads();
+    for (int dy = threadIdx.y; dy < 32; dy += blockDim.y) {
+        const long long o = o0 + dy;
+        const int b = b0 + threadIdx.x;
+        if (o < L && b < Bpad) gT[static_cast<size_t>(o) * Bpad + b] = tile[threadIdx.x][dy];
+    }
+}
+
+}  // namespace
+
+size_t grad_x_workspace_bytes(const ffi_plan* plan, int64_t B) {
+    DeviceInfo dev;
+    if (get_device_info(&dev) != FFI_OK) return 0;
+    NarrowConfig c;
+    if (narrow_config(plan, B, dev, &c))
+        return static_cast<size_t>(c.R) * plan->N * c.Bpad * 4;
+    const size_t Bpad = static_cast<size_t>(round_up(B, 128));
+    return static_cast<size_t>(plan->L) * Bpad * 4;
+}
+
+int launch_grad_x(const GradXArgs& a, cudaStream_t stream) {
+    DeviceInfo dev;
+    int rc = get_device_info(&dev);
+    if (rc != FFI_OK) return rc;
+    const ffi_plan* plan = a.plan;
+    const size_t need = grad_x_workspace_bytes(plan, a.B);
+    if (!a.workspace || a.workspace_bytes < need)
+        return fail(FFI_ERR_WORKSPACE, "grad_x needs %zu bytes of workspace, got %zu", need, a.workspace_bytes);
+    if (reinterpret_cast<uintptr_t>(a.workspace) % 16 != 0)
+        return fail(FFI_ERR_WORKSPACE, "workspace must be 16-byte aligned");
+
+    NarrowConfig c;
+    if (narrow_config(plan, a.B, dev, &c)) {
+        GxNarrowParams p;
+        p.W = a.W;
+        p.g = a.g;
+        p.cperm = plan->cperm;
+        p.cptr = plan->cptr;
+        p.partial = static_cast<float*>(a.workspace);
+        p.B = a.B;
+        p.N = a.N;
+        p.L = a.L;
+        p.K = a.K;
+        p.T = plan->chunk_rows;
+        p.nChunks = plan->n_chunks;
+        p.R = c.R;
+        p.Bpad = c.Bpad;
+        p.entCap = c.entCap;
+        if (c.bpl == 4) rc = launch_narrow_t<16, 4>(p, c.smem, c.iparts, c.nBT, stream);
+        else if (c.bpl == 2) rc = launch_narrow_t<32, 2>(p, c.smem, c.iparts, c.nBT, stream);
+        else rc = launch_narrow_t<64, 1>(p, c.smem, c.iparts, c.nBT, stream);
+        if (rc != FFI_OK) return rc;
+        const long long total = static_cast<long long>(a.N) * c.Bpad;
+        reduce_partials_kernel<<<static_cast<unsigned>(ceil_div(total, 256)), 256, 0, stream>>>(
+            p.partial, a.gx, c.R, a.N, a.B, c.Bpad, a.x_transposed);
+        FFI_LAUNCH_CHECK("reduce_partials_kernel");
+        return FFI_OK;
+    }
+
+    // Wide inputs.
+    const int Bpad = static_cast<int>(round_up(a.B, 128));
+    float* gT = static_cast<float*>(a.workspace);
+    {
+        dim3 block(32, 8);
+        const long long gx_blocks = ceil_div(a.L, 32);
+        if (gx_blocks > 2147483647LL) return fail(FFI_ERR_UNSUPPORTED, "L too large");
+        dim3 grid(static_cast<unsigned>(gx_blocks), static_cast<unsigned>(Bpad / 32));
+        transpose_g_kernel<<<grid, block, 0, stream>>>(a.g, gT, a.B, a.L, Bpad);
+        FFI_LAUNCH_CHECK("transpose_g_kernel");
+    }
+    const long long warps = static_cast<long long>(a.N) * (Bpad / 128);
+    ffi_grad_x_wide_kernel<<<static_cast<unsigned>(ceil_div(warps, 8)), 256, 0, stream>>>(
+        a.W, gT, plan->rowptr, plan->perm, a.gx, a.B, a.N, a.K, Bpad, a.x_transposed);
+    FFI_LAUNCH_CHECK("ffi_grad_x_wide_kernel");
+    return FFI_OK;
+}
+
+}  // namespace ffi

@@ -1,0 +1,381 @@
+// Transposed (CSR-by-input) index of an FFI index table, built on the device.
+//
+// The reference has no such structure: its grad_x scatters with atomicAdd
+// (tfsparse/cc/kernels/backward.cu.h:119-182).  Definition (bit-exact contract):
+// flat position p = o*K + k; `perm` lists all positions ordered by key idx[p]
+// ascending, ties by p ascending; rowptr[i] = number of positions with key < i.
+//
+// Build: a stable least-significant-digit radix sort of (key, position) pairs, 8 bits
+// per pass, one warp per 1024-element tile (per-tile digit histogram, global exclusive
+// scan, stable in-tile ranking with warp match).  From the canonical form a chunked
+// form is derived for the narrow-input grad_x kernel: the outputs are cut into chunks
+// of T rows, and chunk c stores its T*K positions ordered by (key, position) in
+// cperm[c*T*K ...], with cptr[c][i] the offset of input i's run inside the chunk.
+// Concatenating, for each input i, its runs over the chunks in chunk order gives back
+// exactly row i of the canonical form (chunks are ascending ranges of p).
+#include "ffi_common.cuh"
+
+namespace ffi {
+namespace {
+
+constexpr int kTile = 1024;      // elements per warp tile
+constexpr int kSortWarps = 4;    // warps per block in the sort kernels
+
+__global__ void validate_idx_kernel(const int* __restrict__ idx, long long n, int N, int* bad) {
+    long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    bool any = false;
+    for (; e < n; e += stride) {
+        unsigned v = static_cast<unsigned>(idx[e]);
+        any |= v >= static_cast<unsigned>(N);
+    }
+    if (any) *bad = 1;
+}
+
+// counts[d * nTiles + tile] = number of elements of `tile` whose digit is d.
+__global__ void radix_hist_kernel(const int* __restrict__ keys, long long n, int shift,
+                                  int* __restrict__ counts, long long nTiles) {
+    __shared__ int h[kSortWarps][256];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long tile = static_cast<long long>(blockIdx.x) * kSortWarps + warp;
+    for (int d = lane; d < 256; d += 32) h[warp][d] = 0;
+    __syncwarp();
+    if (tile < nTiles) {
+        const long long base = tile * kTile;
+        for (int r = 0; r < kTile / 32; ++r) {
+            long long e = base + r * 32 + lane;
+            if (e < n) atomicAdd(&h[warp][(keys[e] >> shift) & 255], 1);
+        }
+        __syncwarp();
+        for (int d = lane; d < 256; d += 32) counts[static_cast<long long>(d) * nTiles + tile] = h[warp][d];
+    }
+}
+
+// In-place exclusive scan of `data[0..n)` by one block; int64 running total, int32 output
+// (totals are bounded by L*K < 2^31).
+__global__ void exclusive_scan_kernel(int* __restrict__ data, long long n) {
+    __shared__ long long sums[1024];
+    const int t = threadIdx.x;
+    const long long chunk = (n + blockDim.x - 1) / blockDim.x;
+    const long long lo = min(n, t * chunk), hi = min(n, lo + chunk);
+    long long s = 0;
+    for (long long e = lo; e < hi; ++e) s += data[e];
+    sums[t] = s;
+    __syncthreads();
+    if (t == 0) {
+        long long run = 0;
+        for (int j = 0; j < blockDim.x; ++j) {
+            long long v = sums[j];
+            sums[j] = run;
+            run += v;
+        }
+    }
+    __syncthreads();
+    long long run = sums[t];
+    for (long long e = lo; e < hi; ++e) {
+        int v = data[e];
+        data[e] = static_cast<int>(run);
+        run += v;
+    }
+}
+
+// Stable scatter of one digit pass. vals_in == nullptr means "value = element index".
+__global__ void radix_scatter_kernel(const int* __restrict__ keys_in, const int* __restrict__ vals_in,
+                                     int* __restrict__ keys_out, int* __restrict__ vals_out,
+                                     long long n, int shift, const int* __restrict__ offsets,
+                                     long long nTiles) {
+    __shared__ int base[kSortWarps][256];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long tile = static_cast<long long>(blockIdx.x) * kSortWarps + warp;
+    if (tile >= nTiles) return;
+    for (int d = lane; d < 256; d += 32) base[warp][d] = offsets[static_cast<long long>(d) * nTiles + tile];
+    __syncwarp();
+    const long long first = tile * kTile;
+    const unsigned lt = (1u << lane) - 1u;
+    for (int r = 0; r < kTile / 32; ++r) {
+        const long long e = first + r * 32 + lane;
+        const bool valid = e < n;
+        const unsigned active = __ballot_sync(0xffffffffu, valid);
+        if (valid) {
+            const int key = keys_in[e];
+            const int val = vals_in ? vals_in[e] : static_cast<int>(e);
+            const int d = (key >> shift) & 255;
+            const unsigned same = __match_any_sync(active, d);
+            const int rank = __popc(same & lt);
+            const int dst = base[warp][d] + rank;
+            __syncwarp(active);
+            if (rank == 0) base[warp][d] += __popc(same);
+            keys_out[dst] = key;
+            vals_out[dst] = val;
+        }
+        __syncwarp();
+    }
+}
+
+// rowptr[i] = lower_bound(sorted_keys, i), i in [0, N].
+__global__ void rowptr_kernel(const int* __restrict__ sorted_keys, long long n, int N,
+                              int* __restrict__ rowptr) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i > N) return;
+    long long lo = 0, hi = n;
+    while (lo < hi) {
+        long long mid = (lo + hi) >> 1;
+        if (sorted_keys[mid] < i) lo = mid + 1;
+        else hi = mid;
+    }
+    rowptr[i] = static_cast<int>(lo);
+}
+
+// lb[c][i] = first position e in row i of the canonical form with perm[e] >= c*T*K.
+__global__ void chunk_bounds_kernel(const int* __restrict__ rowptr, const int* __restrict__ perm,
+                                    int N, long long chunkEntries, long long nChunks,
+                                    int* __restrict__ lb) {
+    const long long id = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (id >= (nChunks + 1) * N) return;
+    const long long c = id / N;
+    const int i = static_cast<int>(id - c * N);
+    const long long target = c * chunkEntries;
+    int lo = rowptr[i], hi = rowptr[i + 1];
+    while (lo < hi) {
+        int mid = (lo + hi) >> 1;
+        if (perm[mid] < target) lo = mid + 1;
+        else hi = mid;
+    }
+    lb[id] = lo;
+}
+
+// One block per chunk: cptr[c][0..N] = exclusive scan over i of the run lengths, and the
+// runs themselves are copied into cperm.
+__global__ void chunk_fill_kernel(const int* __restrict__ perm, const int* __restrict__ lb, int N,
+                                  long long chunkEntries, int* __restrict__ cptr,
+                                  int* __restrict__ cperm) {
+    extern __shared__ int run_off[];  // N + 1
+    const long long c = blockIdx.x;
+    const int* lb0 = lb + c * N;
+    const int* lb1 = lb + (c + 1) * N;
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int i = 0; i < N; ++i) {
+            run_off[i] = run;
+            run += lb1[i] - lb0[i];
+        }
+        run_off[N] = run;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i <= N; i += blockDim.x) cptr[c * (N + 1) + i] = run_off[i];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    int* dst = cperm + c * chunkEntries;
+    for (int i = warp; i < N; i += nwarps) {
+        const int s = lb0[i], len = lb1[i] - s, off = run_off[i];
+        for (int r = lane; r < len; r += 32) dst[off + r] = perm[s + r];
+    }
+}
+
+// Self-check export: rebuild the canonical form from (cptr, cperm).
+__global__ void chunked_row_totals_kernel(const int* __restrict__ cptr, int N, long long nChunks,
+                                          int* __restrict__ totals) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i > N) return;
+    if (i == N) {
+        totals[N] = 0;
+        return;
+    }
+    long long s = 0;
+    for (long long c = 0; c < nChunks; ++c) s += cptr[c * (N + 1) + i + 1] - cptr[c * (N + 1) + i];
+    totals[i] = static_cast<int>(s);
+}
+
+__global__ void chunked_gather_kernel(const int* __restrict__ cptr, const int* __restrict__ cperm,
+                                      const int* __restrict__ rowptr, int N, long long nChunks,
+                                      long long chunkEntries, int* __restrict__ perm_out) {
+    const int lane = threadIdx.x & 31;
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (i >= N) return;
+    long long run = rowptr[i];
+    for (long long c = 0; c < nChunks; ++c) {
+        const int s = cptr[c * (N + 1) + i], len = cptr[c * (N + 1) + i + 1] - s;
+        const int* src = cperm + c * chunkEntries + s;
+        for (int r = lane; r < len; r += 32) perm_out[run + r] = src[r];
+        run += len;
+    }
+}
+
+int significant_bits(int64_t n) {
+    int bits = 0;
+    while ((static_cast<int64_t>(1) << bits) < n) ++bits;
+    return bits < 1 ? 1 : bits;
+}
+
+struct DeviceBuffer {
+    void* ptr = nullptr;
+    ~DeviceBuffer() {
+        if (ptr) cudaFree(ptr);
+    }
+    cudaError_t alloc(size_t bytes) { return cudaMalloc(&ptr, bytes ? bytes : 4); }
+    template <class T>
+    T* as() {
+        return static_cast<T*>(ptr);
+    }
+};
+
+}  // namespace
+
+// Rows per chunk of the chunked lists: the grad_x kernel keeps, per chunk, a g tile of
+// T x 128 floats and up to T*K staged (weight, row) pairs in shared memory.
+int plan_chunk_rows(int64_t K) {
+    const int64_t budget = 200 * 1024;
+    int64_t T = budget / (512 + 8 * K);
+    if (T > 256) T = 256;
+    T = T / 8 * 8;
+    return static_cast<int>(T);
+}
+
+constexpr int64_t kNarrowMaxN = 2048;  // inputs the register-accumulator grad_x kernel covers
+
+}  // namespace ffi
+
+using namespace ffi;
+
+extern "C" int ffi_plan_create(const int32_t* idx, int64_t L, int64_t K, int64_t N, void* stream_v,
+                               ffi_plan** out_plan) {
+    if (!out_plan) return fail(FFI_ERR_INVALID_ARGUMENT, "out_plan is NULL");
+    *out_plan = nullptr;
+    if (!idx) return fail(FFI_ERR_INVALID_ARGUMENT, "idx is NULL");
+    if (L <= 0 || K <= 0 || N <= 0) return fail(FFI_ERR_INVALID_ARGUMENT, "L, K, N must be positive");
+    if (N >= (1LL << 31) || L * K >= (1LL << 31) - kTile)
+        return fail(FFI_ERR_UNSUPPORTED, "L*K=%lld (or N) does not fit 32-bit positions", (long long)(L * K));
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const long long n = L * K;
+
+    ffi_plan* plan = new ffi_plan();
+    plan->L = L;
+    plan->K = K;
+    plan->N = N;
+    FFI_CUDA_CHECK(cudaGetDevice(&plan->device));
+    auto cleanup = [&](int rc) {
+        ffi_plan_destroy(plan);
+        return rc;
+    };
+
+    if (cudaMalloc(&plan->rowptr, (N + 1) * sizeof(int)) != cudaSuccess ||
+        cudaMalloc(&plan->perm, n * sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        return cleanup(fail(FFI_ERR_ALLOC, "cudaMalloc of the transposed index failed"));
+    }
+    plan->device_bytes = (N + 1) * sizeof(int) + n * sizeof(int);
+
+    const long long nTiles = ceil_div(n, kTile);
+    DeviceBuffer kA, vA, kB, vB, counts, bad;
+    if (kA.alloc(n * 4) != cudaSuccess || vA.alloc(n * 4) != cudaSuccess || kB.alloc(n * 4) != cudaSuccess ||
+        vB.alloc(n * 4) != cudaSuccess || counts.alloc(256 * nTiles * 4) != cudaSuccess ||
+        bad.alloc(4) != cudaSuccess) {
+        cudaGetLastError();
+        return cleanup(fail(FFI_ERR_ALLOC, "cudaMalloc of sort scratch failed"));
+    }
+
+    FFI_CUDA_CHECK(cudaMemsetAsync(bad.ptr, 0, 4, stream));
+    validate_idx_kernel<<<1024, 256, 0, stream>>>(idx, n, static_cast<int>(N), bad.as<int>());
+    int h_bad = 0;
+    FFI_CUDA_CHECK(cudaMemcpyAsync(&h_bad, bad.ptr, 4, cudaMemcpyDeviceToHost, stream));
+    FFI_CUDA_CHECK(cudaStreamSynchronize(stream));
+    if (h_bad) return cleanup(fail(FFI_ERR_INDEX_RANGE, "idx holds a value outside [0, %lld)", (long long)N));
+
+    const int passes = (significant_bits(N) + 7) / 8;
+    const unsigned sortBlocks = static_cast<unsigned>(ceil_div(nTiles, kSortWarps));
+    const int* kin = idx;
+    const int* vin = nullptr;
+    int* kout = kA.as<int>();
+    int* vout = vA.as<int>();
+    for (int pass = 0; pass < passes; ++pass) {
+        const int shift = 8 * pass;
+        radix_hist_kernel<<<sortBlocks, 32 * kSortWarps, 0, stream>>>(kin, n, shift, counts.as<int>(), nTiles);
+        exclusive_scan_kernel<<<1, 1024, 0, stream>>>(counts.as<int>(), 256 * nTiles);
+        radix_scatter_kernel<<<sortBlocks, 32 * kSortWarps, 0, stream>>>(kin, vin, kout, vout, n, shift,
+                                                                          counts.as<int>(), nTiles);
+        kin = kout;
+        vin = vout;
+        const bool toB = (kout == kA.as<int>());
+        kout = toB ? kB.as<int>() : kA.as<int>();
+        vout = toB ? vB.as<int>() : vA.as<int>();
+    }
+    FFI_LAUNCH_CHECK("radix sort");
+    rowptr_kernel<<<static_cast<unsigned>(ceil_div(N + 1, 256)), 256, 0, stream>>>(kin, n, static_cast<int>(N),
+                                                                                   plan->rowptr);
+    FFI_CUDA_CHECK(cudaMemcpyAsync(plan->perm, vin, n * 4, cudaMemcpyDeviceToDevice, stream));
+    FFI_LAUNCH_CHECK("rowptr_kernel");
+
+    // Chunked lists for the narrow-input grad_x kernel.
+    const int T = plan_chunk_rows(K);
+    const long long nChunks = ceil_div(L, T > 0 ? T : 1);
+    const long long cptrBytes = nChunks * (N + 1) * 4;
+    if (T >= 8 && N <= kNarrowMaxN && cptrBytes <= (512LL << 20) && static_cast<long long>(T) * K <= 65536) {
+        DeviceBuffer lb;
+        if (lb.alloc((nChunks + 1) * N * 4) != cudaSuccess ||
+            cudaMalloc(&plan->cptr, cptrBytes) != cudaSuccess ||
+            cudaMalloc(&plan->cperm, n * 4) != cudaSuccess) {
+            cudaGetLastError();
+            return cleanup(fail(FFI_ERR_ALLOC, "cudaMalloc of the chunked index failed"));
+        }
+        plan->device_bytes += cptrBytes + n * 4;
+        const long long chunkEntries = static_cast<long long>(T) * K;
+        const long long nb = (nChunks + 1) * N;
+        chunk_bounds_kernel<<<static_cast<unsigned>(ceil_div(nb, 256)), 256, 0, stream>>>(
+            plan->rowptr, plan->perm, static_cast<int>(N), chunkEntries, nChunks, lb.as<int>());
+        chunk_fill_kernel<<<static_cast<unsigned>(nChunks), 256, (N + 1) * sizeof(int), stream>>>(
+            plan->perm, lb.as<int>(), static_cast<int>(N), chunkEntries, plan->cptr, plan->cperm);
+        FFI_LAUNCH_CHECK("chunk kernels");
+        FFI_CUDA_CHECK(cudaStreamSynchronize(stream));
+        plan->chunk_rows = T;
+        plan->n_chunks = nChunks;
+        plan->has_chunks = true;
+    }
+    FFI_CUDA_CHECK(cudaStreamSynchronize(stream));
+    *out_plan = plan;
+    return FFI_OK;
+}
+
+extern "C" int ffi_plan_destroy(ffi_plan* plan) {
+    if (!plan) return FFI_OK;
+    if (plan->rowptr) cudaFree(plan->rowptr);
+    if (plan->perm) cudaFree(plan->perm);
+    if (plan->cperm) cudaFree(plan->cperm);
+    if (plan->cptr) cudaFree(plan->cptr);
+    delete plan;
+    return FFI_OK;
+}
+
+extern "C" int ffi_plan_info(const ffi_plan* plan, int64_t* L, int64_t* K, int64_t* N, int64_t* chunk_rows,
+                             int64_t* n_chunks, int64_t* device_bytes) {
+    if (!plan) return fail(FFI_ERR_INVALID_ARGUMENT, "plan is NULL");
+    if (L) *L = plan->L;
+    if (K) *K = plan->K;
+    if (N) *N = plan->N;
+    if (chunk_rows) *chunk_rows = plan->has_chunks ? plan->chunk_rows : 0;
+    if (n_chunks) *n_chunks = plan->has_chunks ? plan->n_chunks : 0;
+    if (device_bytes) *device_bytes = static_cast<int64_t>(plan->device_bytes);
+    return FFI_OK;
+}
+
+extern "C" int ffi_plan_export(const ffi_plan* plan, int32_t* rowptr, int32_t* perm, void* stream_v) {
+    if (!plan || !rowptr || !perm) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL argument to ffi_plan_export");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    FFI_CUDA_CHECK(cudaMemcpyAsync(rowptr, plan->rowptr, (plan->N + 1) * 4, cudaMemcpyDeviceToDevice, stream));
+    FFI_CUDA_CHECK(cudaMemcpyAsync(perm, plan->perm, plan->L * plan->K * 4, cudaMemcpyDeviceToDevice, stream));
+    return FFI_OK;
+}
+
+extern "C" int ffi_plan_export_chunked(const ffi_plan* plan, int32_t* rowptr, int32_t* perm, void* stream_v) {
+    if (!plan || !rowptr || !perm)
+        return fail(FFI_ERR_INVALID_ARGUMENT, "NULL argument to ffi_plan_export_chunked");
+    if (!plan->has_chunks) return fail(FFI_ERR_UNSUPPORTED, "plan has no chunked lists (wide N)");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const int N = static_cast<int>(plan->N);
+    chunked_row_totals_kernel<<<static_cast<unsigned>(ceil_div(N + 1, 256)), 256, 0, stream>>>(
+        plan->cptr, N, plan->n_chunks, rowptr);
+    exclusive_scan_kernel<<<1, 1024, 0, stream>>>(rowptr, N + 1);
+    chunked_gather_kernel<<<static_cast<unsigned>(ceil_div(N, 4)), 128, 0, stream>>>(
+        plan->cptr, plan->cperm, rowptr, N, plan->n_chunks,
+        static_cast<long long>(plan->chunk_rows) * plan->K, perm);
+    FFI_LAUNCH_CHECK("chunked export");
+    return FFI_OK;
+}

@@ -1,0 +1,244 @@
+"""Host-side mirror of the reference's Python op binding (sparse/ops/fixed_fan_in_ops.py).
+
+Same function names, argument order and return values as the reference's wrappers
+(fixed_fan_in_ops.py:15-28), over torch CUDA tensors instead of TensorFlow tensors:
+
+* ``fan_in_sparse_matmul(features[B,N], lookup[L,K], weights[L,K]) -> [B,L]``
+* ``fan_in_sparse_matmul_tp(features[N,B], lookup, weights) -> [B,L]``
+* ``fan_in_sparse_matmul_grad(features, lookup, weights, out_grad) -> (feature_grad, weight_grad)``
+* ``fan_in_sparse_matmul_grad_tp(...)`` likewise for the transposed layout
+
+and the gradient wiring of fixed_fan_in_ops.py:31-40 (``[feature_grad, None, weight_grad]``)
+as :class:`torch.autograd.Function` objects behind ``ffi_matmul`` / ``ffi_matmul_tp``.
+Every call goes through the C ABI of ``libffi_b200.so``; there is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes
+import weakref
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_workspaces: dict = {}
+_plan_cache: dict = {}
+_PLAN_CACHE_MAX = 8
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _workspace(device, nbytes: int) -> Optional[torch.Tensor]:
+    """A cached scratch buffer of at least nbytes on `device` (grown, never shrunk)."""
+    if nbytes <= 0:
+        return None
+    key = (device.index, _stream_ptr(device))
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(int(nbytes * 1.25) + 256, dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def _check_cuda(name: str, t: torch.Tensor, dtypes) -> torch.Tensor:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor: this library has no CPU path")
+    if t.dtype not in dtypes:
+        raise TypeError(f"{name} has dtype {t.dtype}, expected one of {dtypes}")
+    if t.dim() != 2:
+        raise ValueError(f"{name} must have rank 2, got shape {tuple(t.shape)}")
+    return t.contiguous()
+
+
+_INDEX_DTYPES = (torch.int32, torch.uint32) if hasattr(torch, "uint32") else (torch.int32,)
+
+
+def _as_index(lookup: torch.Tensor) -> torch.Tensor:
+    lookup = _check_cuda("lookup", lookup, _INDEX_DTYPES)
+    if lookup.dtype != torch.int32:
+        lookup = lookup.view(torch.int32)  # values < 2^31 by the reference's contract
+    return lookup
+
+
+def _shapes(features, lookup, weights, transposed):
+    if lookup.shape != weights.shape:
+        raise ValueError(f"lookup {tuple(lookup.shape)} and weights {tuple(weights.shape)} must have equal shapes")
+    if transposed:
+        N, B = features.shape
+    else:
+        B, N = features.shape
+    L, K = lookup.shape
+    return B, N, L, K
+
+
+class FFIPlan:
+    """Transposed (CSR-by-input) index of one lookup table; owns device memory.
+
+    Build one per lookup table and rebuild it whenever the table changes (rewiring).
+    """
+
+    def __init__(self, lookup: torch.Tensor, n_in: int):
+        lookup = _as_index(lookup)
+        self.device = lookup.device
+        self.L, self.K = (int(s) for s in lookup.shape)
+        self.N = int(n_in)
+        handle = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().ffi_plan_create(lookup.data_ptr(), self.L, self.K, self.N,
+                                                   _stream_ptr(self.device), ctypes.byref(handle)))
+        self._handle = handle
+        self._finalizer = weakref.finalize(self, _lib.load().ffi_plan_destroy, handle)
+
+    @property
+    def handle(self):
+        return self._handle
+
+    def info(self) -> dict:
+        vals = [ctypes.c_int64() for _ in range(6)]
+        _lib.check(_lib.load().ffi_plan_info(self._handle, *[ctypes.byref(v) for v in vals]))
+        names = ("L", "K", "N", "chunk_rows", "n_chunks", "device_bytes")
+        return {n: int(v.value) for n, v in zip(names, vals)}
+
+    def export(self, chunked: bool = False):
+        """(rowptr[N+1], perm[L*K]) int32 device tensors of the canonical transposed index."""
+        rowptr = torch.empty(self.N + 1, dtype=torch.int32, device=self.device)
+        perm = torch.empty(self.L * self.K, dtype=torch.int32, device=self.device)
+        fn = _lib.load().ffi_plan_export_chunked if chunked else _lib.load().ffi_plan_export
+        with torch.cuda.device(self.device):
+            _lib.check(fn(self._handle, rowptr.data_ptr(), perm.data_ptr(), _stream_ptr(self.device)))
+        return rowptr, perm
+
+    def close(self):
+        self._finalizer()
+
+
+def get_plan(lookup: torch.Tensor, n_in: int) -> FFIPlan:
+    """Plan for `lookup`, cached per (storage, shape, tensor version): an in-place update of
+    the table (rewiring) bumps the tensor's version and leads to a rebuild."""
+    key = (lookup.data_ptr(), tuple(lookup.shape), int(n_in), lookup.device.index)
+    hit = _plan_cache.get(key)
+    if hit is not None and hit[0] == lookup._version:
+        return hit[1]
+    plan = FFIPlan(lookup, n_in)
+    if len(_plan_cache) >= _PLAN_CACHE_MAX:
+        _plan_cache.pop(next(iter(_plan_cache)))
+    _plan_cache[key] = (lookup._version, plan)
+    return plan
+
+
+def clear_caches():
+    _plan_cache.clear()
+    _workspaces.clear()
+
+
+def _forward(features, lookup, weights, bias, transposed: bool) -> torch.Tensor:
+    features = _check_cuda("features", features, (torch.float32,))
+    weights = _check_cuda("weights", weights, (torch.float32,))
+    lookup = _as_index(lookup)
+    B, N, L, K = _shapes(features, lookup, weights, transposed)
+    lib = _lib.load()
+    dev = features.device
+    if bias is not None:
+        if bias.shape != (L,) or bias.dtype != torch.float32 or not bias.is_cuda:
+            raise ValueError("bias must be a float32 CUDA tensor of shape [L]")
+        bias = bias.contiguous()
+    out = torch.empty((B, L), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        ws_bytes = lib.ffi_forward_workspace_bytes(B, N, L, K, int(transposed), _lib.FFI_F32)
+        ws = _workspace(dev, ws_bytes)
+        _lib.check(lib.ffi_forward(features.data_ptr(), lookup.data_ptr(), weights.data_ptr(),
+                                   bias.data_ptr() if bias is not None else None, out.data_ptr(),
+                                   B, N, L, K, int(transposed), _lib.FFI_F32,
+                                   ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                                   _stream_ptr(dev)))
+    return out
+
+
+def _backward(features, lookup, weights, out_grad, transposed: bool, plan: Optional[FFIPlan] = None,
+              want_feature_grad=True, want_weight_grad=True, want_bias_grad=False):
+    features = _check_cuda("features", features, (torch.float32,))
+    weights = _check_cuda("weights", weights, (torch.float32,))
+    out_grad = _check_cuda("out_grad", out_grad, (torch.float32,))
+    lookup = _as_index(lookup)
+    B, N, L, K = _shapes(features, lookup, weights, transposed)
+    if tuple(out_grad.shape) != (B, L):
+        raise ValueError(f"out_grad has shape {tuple(out_grad.shape)}, expected {(B, L)}")
+    lib = _lib.load()
+    dev = features.device
+    if want_feature_grad and plan is None:
+        plan = get_plan(lookup, N)
+    gx = torch.empty_like(features) if want_feature_grad else None
+    gw = torch.empty_like(weights) if want_weight_grad else None
+    gb = torch.empty((L,), dtype=torch.float32, device=dev) if want_bias_grad else None
+    with torch.cuda.device(dev):
+        handle = plan.handle if plan is not None else None
+        ws_bytes = lib.ffi_backward_workspace_bytes(handle, B, N, L, K, int(transposed), _lib.FFI_F32,
+                                                    int(want_feature_grad), int(want_weight_grad or want_bias_grad))
+        ws = _workspace(dev, ws_bytes + 256 if ws_bytes else 0)
+        ws_ptr = None
+        ws_len = 0
+        if ws is not None:
+            off = (-ws.data_ptr()) % 256
+            ws_ptr = ws.data_ptr() + off
+            ws_len = ws.numel() - off
+        _lib.check(lib.ffi_backward(features.data_ptr(), lookup.data_ptr(), weights.data_ptr(), out_grad.data_ptr(),
+                                    handle, gx.data_ptr() if gx is not None else None,
+                                    gw.data_ptr() if gw is not None else None,
+                                    gb.data_ptr() if gb is not None else None,
+                                    B, N, L, K, int(transposed), _lib.FFI_F32, ws_ptr, ws_len, _stream_ptr(dev)))
+    return gx, gw, gb
+
+
+# ---- the reference's four wrappers (sparse/ops/fixed_fan_in_ops.py:15-28) -------------
+
+def fan_in_sparse_matmul(features, lookup, weights):
+    return _forward(features, lookup, weights, None, False)
+
+
+def fan_in_sparse_matmul_tp(features, lookup, weights):
+    return _forward(features, lookup, weights, None, True)
+
+
+def fan_in_sparse_matmul_grad(features, lookup, weights, out_grad):
+    gx, gw, _ = _backward(features, lookup, weights, out_grad, False)
+    return gx, gw
+
+
+def fan_in_sparse_matmul_grad_tp(features, lookup, weights, out_grad):
+    gx, gw, _ = _backward(features, lookup, weights, out_grad, True)
+    return gx, gw
+
+
+# ---- gradient registration (sparse/ops/fixed_fan_in_ops.py:31-40) ---------------------
+
+class _FanInSparseMatmul(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, features, lookup, weights, bias, transposed):
+        ctx.save_for_backward(features, lookup, weights)
+        ctx.transposed = transposed
+        ctx.has_bias = bias is not None
+        return _forward(features, lookup, weights, bias, transposed)
+
+    @staticmethod
+    def backward(ctx, grad):
+        features, lookup, weights = ctx.saved_tensors
+        need_x, _, need_w = ctx.needs_input_grad[:3]
+        need_b = ctx.has_bias and ctx.needs_input_grad[3]
+        gx, gw, gb = _backward(features, lookup, weights, grad.contiguous(), ctx.transposed,
+                               want_feature_grad=need_x, want_weight_grad=need_w, want_bias_grad=need_b)
+        return gx, None, gw, gb, None
+
+
+def ffi_matmul(features, lookup, weights, bias=None):
+    """Differentiable FanInSparseMatmul (+ optional fused bias)."""
+    return _FanInSparseMatmul.apply(features, lookup, weights, bias, False)
+
+
+def ffi_matmul_tp(features, lookup, weights, bias=None):
+    """Differentiable FanInSparseMatmulTp (features given as [N,B]) (+ optional fused bias)."""
+    return _FanInSparseMatmul.apply(features, lookup, weights, bias, True)

@@ -1,0 +1,155 @@
+/*
+ * C ABI of the B200 (sm_100a) fixed-fan-in (FFI) sparse layer.
+ *
+ *   y[b,o]     = bias[o] + sum_k W[o,k] * x[b, idx[o,k]]
+ *   grad_W[o,k] = sum_b g[b,o] * x[b, idx[o,k]]
+ *   grad_x[b,i] = sum over (o,k) with idx[o,k]==i of W[o,k] * g[b,o]
+ *   grad_b[o]   = sum_b g[b,o]
+ *
+ * Every pointer is a DEVICE pointer unless said otherwise; the caller owns all
+ * tensors and every workspace.  All work is enqueued on `stream` (a cudaStream_t
+ * passed as void*); no call synchronises the device except the plan functions,
+ * which say so.  Every function returns an ffi_status; ffi_last_error() gives the
+ * text of the calling thread's last failure.  Nothing here aborts the process.
+ *
+ * Layouts are the reference's (tfsparse/cc/kernels/kernel_data.cu.h:197-225), all
+ * row-major: x is [B,N], or [N,B] when x_transposed != 0; idx and W are [L,K];
+ * y and g are [B,L]; grad_x has the layout of x; grad_W the layout of W.
+ * idx holds int32 or uint32 values in [0,N) (both index types the reference
+ * registers, tfsparse/cc/kernels/register.cpp:79-109, share these entry points
+ * because values are < 2^31 by the reference's contract, forward.cu:24-28).
+ * Duplicate indices within a row are legal and add.
+ */
+#ifndef FFI_B200_H
+#define FFI_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ffi_status {
+    FFI_OK = 0,
+    FFI_ERR_INVALID_ARGUMENT = 1, /* null pointer, non-positive or oversize dimension */
+    FFI_ERR_UNSUPPORTED = 2,      /* dtype / shape outside what the kernels cover */
+    FFI_ERR_WORKSPACE = 3,        /* workspace missing or too small */
+    FFI_ERR_CUDA = 4,             /* a CUDA runtime call or launch failed */
+    FFI_ERR_STALE_PLAN = 5,       /* plan does not match (L,K,N) of the call */
+    FFI_ERR_INDEX_RANGE = 6,      /* an index outside [0,N) was found while planning */
+    FFI_ERR_ALLOC = 7             /* device allocation failed while planning */
+} ffi_status;
+
+/* Storage type of x and W.  Accumulation, bias, y, g and all gradients are fp32. */
+typedef enum ffi_dtype { FFI_F32 = 0, FFI_BF16 = 1 } ffi_dtype;
+
+typedef struct ffi_plan ffi_plan; /* opaque: transposed (CSR-by-input) index of one idx table */
+
+/* Text of the calling thread's most recent error ("" if none). Host pointer. */
+const char* ffi_last_error(void);
+
+/* Library ABI version (major*100 + minor). */
+int ffi_version(void);
+
+/* ---------------------------------------------------------------- forward ---- */
+
+/* Bytes of scratch ffi_forward needs for this shape (0 when none is needed). */
+size_t ffi_forward_workspace_bytes(int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed,
+                                   int dtype);
+
+/*
+ * y = FFI(x, idx, W) (+ bias when bias != NULL).
+ * Replaces FixedFanInSparseMatmulKernel<GPUDevice,...>::operator()
+ * (tfsparse/cc/kernels/forward.cu:35-74) as called from
+ * FixedFanInSparseMatmulOp::Compute (tfsparse/cc/kernels/register.cpp:18-39):
+ * x_transposed=0 is op "FanInSparseMatmul", x_transposed=1 is "FanInSparseMatmulTp".
+ * The optional bias replaces the separate tf.nn.bias_add of sparse/layer.py:245-247.
+ */
+int ffi_forward(const void* x, const int32_t* idx, const void* W, const float* bias, float* y,
+                int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed, int dtype,
+                void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------- plan ---- */
+
+/*
+ * Builds the transposed index of `idx` on the device: a stable sort of the flat
+ * positions p = o*K+k by key idx[p] (ties by p), plus the chunked form the grad_x
+ * kernel walks.  Allocates device memory owned by the plan, and synchronises
+ * `stream` once (to report FFI_ERR_INDEX_RANGE).  Call again whenever idx changes
+ * (the reference rewires idx in sparse/custom_layer.py:32-43).  No counterpart in
+ * the reference, whose grad_x uses atomicAdd (tfsparse/cc/kernels/backward.cu.h:119-182).
+ */
+int ffi_plan_create(const int32_t* idx, int64_t L, int64_t K, int64_t N, void* stream,
+                    ffi_plan** out_plan);
+
+int ffi_plan_destroy(ffi_plan* plan);
+
+/* Host-side description of a plan. Any out pointer may be NULL. */
+int ffi_plan_info(const ffi_plan* plan, int64_t* L, int64_t* K, int64_t* N, int64_t* chunk_rows,
+                  int64_t* n_chunks, int64_t* device_bytes);
+
+/*
+ * Copies the canonical transposed index into caller buffers: rowptr[N+1], perm[L*K]
+ * (int32, device).  rowptr[i] = number of entries with key < i; perm lists positions
+ * by (key, position) ascending.
+ */
+int ffi_plan_export(const ffi_plan* plan, int32_t* rowptr, int32_t* perm, void* stream);
+
+/* Same, but re-derived from the chunked lists the grad_x kernel reads (a self-check). */
+int ffi_plan_export_chunked(const ffi_plan* plan, int32_t* rowptr, int32_t* perm, void* stream);
+
+/* --------------------------------------------------------------- backward ---- */
+
+/* Bytes of scratch ffi_backward needs. `plan` may be NULL when want_grad_x == 0. */
+size_t ffi_backward_workspace_bytes(const ffi_plan* plan, int64_t B, int64_t N, int64_t L, int64_t K,
+                                    int x_transposed, int dtype, int want_grad_x, int want_grad_w);
+
+/*
+ * grad_x, grad_W and (optionally) grad_bias from the upstream gradient g[B,L].
+ * Any of grad_x / grad_w / grad_bias may be NULL to skip it.  grad_x needs `plan`
+ * (built from this idx); it is computed over the transposed index, without atomics,
+ * in a summation order that depends only on (idx, shape), so it is bit-reproducible.
+ * Replaces FixedFanInSparseMatmulGradKernel<GPUDevice,...>::operator()
+ * (tfsparse/cc/kernels/backward.cu:87-133) as called from
+ * FixedFanInSparseMatmulGradOp::Compute (tfsparse/cc/kernels/register.cpp:48-72):
+ * x_transposed=0 is op "FanInSparseMatmulGrad", 1 is "FanInSparseMatmulGradTp".
+ * grad_bias replaces TensorFlow's BiasAddGrad for sparse/layer.py:247.
+ */
+int ffi_backward(const void* x, const int32_t* idx, const void* W, const float* g,
+                 const ffi_plan* plan, float* grad_x, float* grad_w, float* grad_bias, int64_t B,
+                 int64_t N, int64_t L, int64_t K, int x_transposed, int dtype, void* workspace,
+                 size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------ loss / Adam ---- */
+
+/*
+ * Sigmoid binary cross-entropy against sparse multi-hot targets (CSR: row_ptr[B+1],
+ * labels[nnz], device int32; labels of one row distinct).
+ *   g[b,o]  = (sigmoid(z[b,o]) - t[b,o]) / (B * L_total)          (may alias z)
+ *   *loss   = (1/(B*L_total)) * sum (max(z,0) - z*t + log1p(exp(-|z|)))   (device float, may be NULL)
+ * L_total is the full label count the mean runs over; it differs from L when z is one
+ * label shard [B,L] whose first label has global id label_offset (labels outside the
+ * shard are ignored).  Replaces SparseBinaryCrossEntropyLoss (sparse/metrics.py:132-139,
+ * 167-173 with sparse/utils.py:15-21) plus the Keras batch mean and its gradient.
+ * loss_workspace: at least ffi_bce_workspace_bytes(B, L) bytes.
+ */
+size_t ffi_bce_workspace_bytes(int64_t B, int64_t L);
+int ffi_bce_grad(const float* z, const int32_t* row_ptr, const int32_t* labels, float* g,
+                 float* loss, int64_t B, int64_t L, int64_t L_total, int64_t label_offset,
+                 void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * One Adam step on n weights, fused into one pass: t = step (1-based),
+ *   alpha = lr*sqrt(1-beta2^t)/(1-beta1^t); m += (g-m)(1-beta1); v += (g*g-v)(1-beta2);
+ *   w -= alpha*m/(sqrt(v)+eps).
+ * This is the update of keras.optimizers.Adam, which sparse/optimizer.py:9-12 derives
+ * SparseAdam from (used at run.py:126).  w is fp32 or bf16 (dtype); m, v, grad are fp32.
+ */
+int ffi_adam_step(void* w, float* m, float* v, const float* grad, int64_t n, float lr, float beta1,
+                  float beta2, float eps, int64_t step, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FFI_B200_H */

@@ -1,0 +1,315 @@
+"""GPU parity tests: the CUDA path (through the C ABI) against the CPU oracle, the golden
+fixtures produced by the reference's own CPU kernels, and size-independent properties.
+
+Tolerances: fp32 results within |d| <= 1e-5 + 1e-5*|ref| of the fp64 oracle; against the
+reference's fp32 goldens the reference's own bounds apply (1e-5 forward, 1.5e-5 backward,
+testing/test_case_templates.h:82,139-140) plus the same relative term.  The transposed index
+is compared bit for bit.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import ecml23_sparse_b200 as ffi
+from ecml23_sparse_b200 import _lib, synth
+from cases import (HUGE_SIZE, KAT_IDX, KAT_W, KAT_X, KAT_Y, SMALL_SIZES, assert_close, config_style_inputs,
+                   golden_path, reference_style_inputs, size_id, to_cuda)
+
+pytestmark = pytest.mark.gpu
+
+RTOL = 1e-5
+ATOL = 1e-5
+
+
+def run_forward(dev, x, idx, W, transposed, bias=None):
+    xin = np.ascontiguousarray(x.T) if transposed else x
+    fn = ffi.fan_in_sparse_matmul_tp if transposed else ffi.fan_in_sparse_matmul
+    if bias is None:
+        return fn(to_cuda(xin, dev), to_cuda(idx, dev), to_cuda(W, dev)).cpu().numpy()
+    op = ffi.ffi_matmul_tp if transposed else ffi.ffi_matmul
+    return op(to_cuda(xin, dev), to_cuda(idx, dev), to_cuda(W, dev), to_cuda(bias, dev)).cpu().numpy()
+
+
+def run_backward(dev, x, idx, W, g, transposed):
+    xin = np.ascontiguousarray(x.T) if transposed else x
+    fn = ffi.fan_in_sparse_matmul_grad_tp if transposed else ffi.fan_in_sparse_matmul_grad
+    gx, gw = fn(to_cuda(xin, dev), to_cuda(idx, dev), to_cuda(W, dev), to_cuda(g, dev))
+    gx = gx.cpu().numpy()
+    return (gx.T if transposed else gx), gw.cpu().numpy()
+
+
+def check_against_oracle(dev, x, idx, W, g, transposed, what=""):
+    B, N = x.shape
+    y = run_forward(dev, x, idx, W, transposed)
+    assert_close(y, oracle.forward_f64(x, idx, W), RTOL, ATOL, what + " y")
+    gx, gw = run_backward(dev, x, idx, W, g, transposed)
+    assert_close(gw, oracle.grad_w_f64(x, idx, g), RTOL, ATOL, what + " grad_W")
+    assert_close(gx, oracle.grad_x_f64(idx, W, g, N), RTOL, ATOL, what + " grad_x")
+    return y, gx, gw
+
+
+@pytest.mark.parametrize("transposed", [False, True], ids=["plain", "tp"])
+def test_known_answer_forward_exact(cuda_device, transposed):
+    # testing/test.cpp:13-47: exact equality, both layouts
+    y = run_forward(cuda_device, KAT_X, KAT_IDX, KAT_W, transposed)
+    assert np.array_equal(y, KAT_Y)
+
+
+@pytest.mark.parametrize("size", SMALL_SIZES, ids=size_id)
+@pytest.mark.parametrize("transposed", [False, True], ids=["plain", "tp"])
+def test_reference_fixtures(cuda_device, size, transposed):
+    x, idx, W, g = reference_style_inputs(size)
+    y, gx, gw = check_against_oracle(cuda_device, x, idx, W, g, transposed, size_id(size))
+    gold = np.load(golden_path(size))
+    assert_close(y, gold["y"], RTOL, 1e-5, "y vs reference golden")
+    assert_close(gw, gold["grad_w"], RTOL, 1.5e-5, "grad_W vs reference golden")
+    assert_close(gx, gold["grad_x"], 2e-5, 1.5e-5, "grad_x vs reference golden")
+
+
+def test_reference_fixture_four_million_units(cuda_device):
+    # (1, 32, 4,000,000, 4): the fixture on which the reference's clamped grid skips units
+    # (tfsparse/cc/kernels/kernel_data.cu.h:125-143); every unit must be written here.
+    x, idx, W, g = reference_style_inputs(HUGE_SIZE)
+    B, N, L, K = HUGE_SIZE
+    gold = np.load(golden_path(HUGE_SIZE))
+    s = int(gold["sample_stride"])
+    for transposed in (False, True):
+        y = run_forward(cuda_device, x, idx, W, transposed)
+        assert_close(y, oracle.forward_f64(x, idx, W), RTOL, ATOL, "y")
+        assert_close(y.ravel()[::s], gold["y_sample"], RTOL, 1e-5, "y vs golden sample")
+        gx, gw = run_backward(cuda_device, x, idx, W, g, transposed)
+        assert_close(gw, oracle.grad_w_f64(x, idx, g), RTOL, ATOL, "grad_W")
+        assert_close(gw.ravel()[::s], gold["grad_w_sample"], RTOL, 1.5e-5, "grad_W vs golden sample")
+        assert_close(gx, oracle.grad_x_f64(idx, W, g, N), RTOL, ATOL, "grad_x")
+        # the reference's own fp32 running sum of 500,000 terms carries ~1e-4 relative error
+        assert_close(gx, gold["grad_x"], 5e-4, 1.5e-5, "grad_x vs golden")
+
+
+EXTRA_SHAPES = [
+    # (B, N, L, K)  fan-ins around the vector widths, odd sizes, batch tile edges
+    (5, 7, 33, 1), (9, 10, 50, 3), (31, 129, 300, 32), (33, 130, 301, 33), (64, 64, 257, 64),
+    (65, 255, 1000, 72), (128, 768, 2049, 32), (129, 100, 513, 5), (200, 37, 700, 12), (2, 2, 1, 2),
+    (32, 768, 20_011, 32), (128, 768, 20_011, 32), (256, 512, 4_099, 32),
+]
+
+
+@pytest.mark.parametrize("shape", EXTRA_SHAPES, ids=size_id)
+@pytest.mark.parametrize("transposed", [False, True], ids=["plain", "tp"])
+def test_extra_shapes(cuda_device, shape, transposed):
+    x, idx, W, g = reference_style_inputs(shape, seed=sum(shape), relu_grad=False)
+    check_against_oracle(cuda_device, x, idx, W, g, transposed, size_id(shape))
+
+
+@pytest.mark.parametrize("shape", [(16, 5000, 3000, 8), (130, 3000, 2000, 16), (40, 2500, 1500, 7)], ids=size_id)
+@pytest.mark.parametrize("transposed", [False, True], ids=["plain", "tp"])
+def test_wide_inputs(cuda_device, shape, transposed):
+    # N too large for the shared-memory x tile / register accumulators: the global-memory paths
+    x, idx, W, g = reference_style_inputs(shape, seed=11, relu_grad=False)
+    check_against_oracle(cuda_device, x, idx, W, g, transposed, size_id(shape))
+
+
+def test_benchmark_distribution_inputs(cuda_device):
+    B, N, L, K = 128, 768, 30_000, 32
+    x, idx, W, g = config_style_inputs(B, N, L, K)
+    check_against_oracle(cuda_device, x, idx, W, g, True, "config-style")
+
+
+def test_uint32_indices_and_duplicates(cuda_device):
+    dev = cuda_device
+    x, idx, W, g = reference_style_inputs((17, 12, 63, 44))
+    idx[:, 1] = idx[:, 0]  # force duplicates inside every row
+    y32 = ffi.fan_in_sparse_matmul(to_cuda(x, dev), to_cuda(idx, dev), to_cuda(W, dev))
+    if hasattr(torch, "uint32"):
+        yu = ffi.fan_in_sparse_matmul(to_cuda(x, dev), to_cuda(idx, dev).view(torch.uint32), to_cuda(W, dev))
+        assert torch.equal(y32, yu)
+    assert_close(y32.cpu().numpy(), oracle.forward_f64(x, idx, W), RTOL, ATOL, "y with duplicates")
+    gx, gw = run_backward(dev, x, idx, W, g, False)
+    assert_close(gx, oracle.grad_x_f64(idx, W, g, 12), RTOL, ATOL, "grad_x with duplicates")
+    assert_close(gw, oracle.grad_w_f64(x, idx, g), RTOL, ATOL, "grad_W with duplicates")
+
+
+def test_fused_bias_and_grad_bias(cuda_device):
+    dev = cuda_device
+    x, idx, W, g = reference_style_inputs((65, 255, 1000, 72), relu_grad=False)
+    bias = np.linspace(-2, 2, 1000).astype(np.float32)
+    for transposed in (False, True):
+        y = run_forward(dev, x, idx, W, transposed, bias=bias)
+        assert_close(y, oracle.forward_f64(x, idx, W, bias=bias), RTOL, ATOL, "y + bias")
+    xt, it, wt, bt = to_cuda(x, dev).requires_grad_(), to_cuda(idx, dev), to_cuda(W, dev).requires_grad_(), \
+        to_cuda(bias, dev).requires_grad_()
+    out = ffi.ffi_matmul(xt, it, wt, bt)
+    out.backward(to_cuda(g, dev))
+    assert_close(bt.grad.cpu().numpy(), oracle.grad_bias_f64(g), RTOL, ATOL, "grad_bias")
+    assert_close(wt.grad.cpu().numpy(), oracle.grad_w_f64(x, idx, g), RTOL, ATOL, "grad_W (autograd)")
+    assert_close(xt.grad.cpu().numpy(), oracle.grad_x_f64(idx, W, g, 255), RTOL, ATOL, "grad_x (autograd)")
+
+
+@pytest.mark.parametrize("shape", [(3, 5, 4, 2), (17, 12, 63, 44), (4, 300, 1000, 7), (8, 768, 5000, 32),
+                                   (2, 70_000, 3000, 4)], ids=size_id)
+def test_transposed_index_bit_exact(cuda_device, shape):
+    B, N, L, K = shape
+    idx = reference_style_inputs(shape)[1]
+    plan = ffi.FFIPlan(to_cuda(idx, cuda_device), N)
+    rowptr, perm = plan.export()
+    exp_rowptr, exp_perm = oracle.transpose_index(idx, N)
+    assert np.array_equal(rowptr.cpu().numpy(), exp_rowptr)
+    assert np.array_equal(perm.cpu().numpy(), exp_perm)
+    info = plan.info()
+    assert (info["L"], info["K"], info["N"]) == (L, K, N)
+    if info["chunk_rows"] > 0:
+        rowptr_c, perm_c = plan.export(chunked=True)
+        assert np.array_equal(rowptr_c.cpu().numpy(), exp_rowptr)
+        assert np.array_equal(perm_c.cpu().numpy(), exp_perm)
+    else:
+        assert N > 2048
+    plan.close()
+
+
+def test_plan_rejects_out_of_range_index_and_stale_shape(cuda_device):
+    dev = cuda_device
+    bad = torch.tensor([[0, 9]], dtype=torch.int32, device=dev)
+    with pytest.raises(_lib.FFIError) as e:
+        ffi.FFIPlan(bad, 9)
+    assert e.value.status == 6
+    x, idx, W, g = reference_style_inputs((12, 8, 32, 16))
+    plan = ffi.FFIPlan(to_cuda(idx, dev), 8)
+    from ecml23_sparse_b200.ops import _backward
+    with pytest.raises(_lib.FFIError) as e:
+        _backward(to_cuda(x[:, :7].copy(), dev), to_cuda(idx % 7, dev), to_cuda(W, dev), to_cuda(g, dev), False, plan=plan)
+    assert e.value.status == 5
+
+
+def test_plan_cache_follows_tensor_version(cuda_device):
+    dev = cuda_device
+    x, idx, W, g = reference_style_inputs((12, 8, 32, 16))
+    it = to_cuda(idx, dev)
+    p1 = ffi.get_plan(it, 8)
+    assert ffi.get_plan(it, 8) is p1
+    it[0, 0] = (it[0, 0] + 1) % 8  # rewiring: in-place update bumps the version
+    p2 = ffi.get_plan(it, 8)
+    assert p2 is not p1
+    gx, _ = ffi.fan_in_sparse_matmul_grad(to_cuda(x, dev), it, to_cuda(W, dev), to_cuda(g, dev))
+    assert_close(gx.cpu().numpy(), oracle.grad_x_f64(it.cpu().numpy(), W, g, 8), RTOL, ATOL, "grad_x after rewiring")
+
+
+def test_backward_is_bit_reproducible(cuda_device):
+    dev = cuda_device
+    x, idx, W, g = config_style_inputs(128, 768, 10_000, 32)
+    args = [to_cuda(np.ascontiguousarray(x.T), dev), to_cuda(idx, dev), to_cuda(W, dev), to_cuda(g, dev)]
+    gx1, gw1 = ffi.fan_in_sparse_matmul_grad_tp(*args)
+    gx2, gw2 = ffi.fan_in_sparse_matmul_grad_tp(*args)
+    assert torch.equal(gx1, gx2) and torch.equal(gw1, gw2)
+
+
+def test_sigmoid_bce_gradient(cuda_device):
+    dev = cuda_device
+    B, L = 37, 5003
+    z = (synth.normal(5, 0, (B, L)) * 3).numpy()
+    row_ptr, labels = synth.multi_hot_targets(5, 1, B, L)
+    loss_ref, g_ref = oracle.bce_f64(z, row_ptr.numpy(), labels.numpy())
+    loss, g = ffi.sparse_bce_with_logits(to_cuda(z, dev), row_ptr, labels)
+    assert abs(float(loss) - loss_ref) <= 1e-5 * abs(loss_ref) + 1e-7
+    assert_close(g.cpu().numpy(), g_ref, 2e-5, 1e-12, "bce grad")
+    # label shard: columns [1000, 3000) of the same problem
+    lo, hi = 1000, 3000
+    zs = np.ascontiguousarray(z[:, lo:hi])
+    loss_s, g_s = ffi.sparse_bce_with_logits(to_cuda(zs, dev), row_ptr, labels, total_labels=L, label_offset=lo)
+    assert_close(g_s.cpu().numpy(), g_ref[:, lo:hi], 2e-5, 1e-12, "bce grad (shard)")
+    # in place
+    zt = to_cuda(z, dev)
+    _, g_in = ffi.sparse_bce_with_logits(zt, row_ptr, labels, inplace=True)
+    assert g_in.data_ptr() == zt.data_ptr() and torch.equal(g_in, g)
+
+
+@pytest.mark.parametrize("n", [1, 7, 4096, 100_003])
+def test_fused_adam_matches_oracle(cuda_device, n):
+    dev = cuda_device
+    w0 = synth.normal(1, 0, (n,)).numpy()
+    w = to_cuda(w0.copy(), dev)
+    opt = ffi.FusedAdam([w], lr=1e-3, beta_1=0.9, beta_2=0.999, epsilon=1e-7)
+    wr, mr, vr = w0.astype(np.float64), np.zeros(n), np.zeros(n)
+    for step in range(1, 4):
+        grad = synth.normal(2, step, (n,)).numpy()
+        opt.step([to_cuda(grad, dev)])
+        wr, mr, vr = oracle.adam_f64(wr, mr, vr, grad.astype(np.float64), 1e-3, 0.9, 0.999, 1e-7, step)
+    assert opt.iterations == 3
+    assert_close(w.cpu().numpy(), wr, 1e-5, 1e-6, "adam w")
+    assert_close(opt.m[0].cpu().numpy(), mr, 1e-5, 1e-7, "adam m")
+    assert_close(opt.v[0].cpu().numpy(), vr, 1e-5, 1e-9, "adam v")
+
+
+def test_layer_module_matches_oracle(cuda_device):
+    dev = cuda_device
+    layer = ffi.FFILayer(in_features=96, units=500, fan_in=12, device=dev, seed=3)
+    with torch.no_grad():
+        layer.bias.copy_(torch.linspace(-1, 1, 500, device=dev))
+    x = synth.normal(4, 0, (20, 96)).numpy()
+    xt = to_cuda(x, dev).requires_grad_()
+    y = layer(xt)
+    idx = layer.lookup().cpu().numpy()
+    W = layer.weights().detach().cpu().numpy()
+    bias = layer.bias.detach().cpu().numpy()
+    assert_close(y.detach().cpu().numpy(), oracle.forward_f64(x, idx, W, bias=bias), RTOL, ATOL, "layer y")
+    g = synth.normal(4, 1, (20, 500)).numpy()
+    y.backward(to_cuda(g, dev))
+    assert_close(xt.grad.cpu().numpy(), oracle.grad_x_f64(idx, W, g, 96), RTOL, ATOL, "layer grad_x")
+    assert_close(layer.kernel_weights.grad.view(500, 12).cpu().numpy(), oracle.grad_w_f64(x, idx, g), RTOL, ATOL,
+                 "layer grad_W")
+    assert_close(layer.bias.grad.cpu().numpy(), oracle.grad_bias_f64(g), RTOL, ATOL, "layer grad_bias")
+
+
+def _torch_reference(xT, idx, W, g, chunk=4096):
+    """Plain PyTorch fp64 statement of the layer, chunked over the outputs: (y, grad_x[N,B], grad_W)."""
+    N, B = xT.shape
+    L, K = idx.shape
+    x64 = xT.double()
+    y = torch.empty((B, L), dtype=torch.float64, device=xT.device)
+    gW = torch.empty((L, K), dtype=torch.float64, device=xT.device)
+    gx = torch.zeros((N, B), dtype=torch.float64, device=xT.device)
+    for o0 in range(0, L, chunk):
+        o1 = min(L, o0 + chunk)
+        ii = idx[o0:o1].long()
+        gathered = x64[ii]                                    # [l, K, B]
+        w = W[o0:o1].double()
+        y[:, o0:o1] = torch.einsum("lk,lkb->bl", w, gathered)
+        gc = g[:, o0:o1].double()                             # [B, l]
+        gW[o0:o1] = torch.einsum("bl,lkb->lk", gc, gathered)
+        contrib = w[:, :, None] * gc.t()[:, None, :]          # [l, K, B]
+        gx.index_add_(0, ii.reshape(-1), contrib.reshape(-1, B))
+    return y, gx, gW
+
+
+def test_headline_shape_full_size(cuda_device):
+    """B=128, N=768, L=670,091, K=32 (the benchmark shape) against a PyTorch fp64 reference on the
+    device, a CPU-oracle check on a slice of the outputs, and linearity in x."""
+    dev = cuda_device
+    B, N, L, K = 128, 768, 670_091, 32
+    xT = synth.normal(21, 0, (N, B), device=dev)
+    idx = synth.indices_without_replacement(21, 1, L, K, N, device=dev)
+    W = synth.normal(21, 2, (L, K), std=(1.0 / K) ** 0.5, device=dev)
+    g = synth.normal(21, 3, (B, L), device=dev)
+    y = ffi.fan_in_sparse_matmul_tp(xT, idx, W)
+    gx, gW = ffi.fan_in_sparse_matmul_grad_tp(xT, idx, W, g)
+    y_ref, gx_ref, gW_ref = _torch_reference(xT, idx, W, g)
+
+    def close(a, b, what):
+        err = (a.double() - b).abs()
+        bound = ATOL + RTOL * b.abs()
+        assert bool((err <= bound).all()), f"{what}: max excess {(err - bound).max().item():.3e}"
+
+    close(y, y_ref, "y")
+    close(gW, gW_ref, "grad_W")
+    close(gx, gx_ref, "grad_x")
+    # CPU oracle on a slice of outputs (rows of idx/W are independent for y and grad_W)
+    rows = np.r_[0:64, L // 2:L // 2 + 64, L - 64:L]
+    x_np = xT.t().contiguous().cpu().numpy()
+    idx_s, W_s = idx[rows].cpu().numpy(), W[rows].cpu().numpy()
+    assert_close(y[:, rows].cpu().numpy(), oracle.forward_f64(x_np, idx_s, W_s), RTOL, ATOL, "y slice vs oracle")
+    assert_close(gW[rows].cpu().numpy(), oracle.grad_w_f64(x_np, idx_s, g[:, rows].contiguous().cpu().numpy()),
+                 RTOL, ATOL, "grad_W slice vs oracle")
+    # linearity: FFI(2x) = 2 FFI(x) exactly in binary floating point
+    assert torch.equal(ffi.fan_in_sparse_matmul_tp(xT * 2, idx, W), y * 2)
+    # determinism at full size
+    gx2, gW2 = ffi.fan_in_sparse_matmul_grad_tp(xT, idx, W, g)
+    assert torch.equal(gx, gx2) and torch.equal(gW, gW2)
