@@ -118,16 +118,21 @@ class FFIPlan:
 
 
 def get_plan(lookup: torch.Tensor, n_in: int) -> FFIPlan:
-    """Plan for `lookup`, cached per (storage, shape, tensor version): an in-place update of
-    the table (rewiring) bumps the tensor's version and leads to a rebuild."""
+    """Plan for `lookup`, cached per (storage address, shape, tensor version).
+
+    An in-place update of the table (rewiring) bumps the tensor's version and leads to a
+    rebuild.  The cache keeps a reference to the table so that its address cannot be handed
+    to another tensor while the entry lives (at most 8 tables are kept).
+    """
     key = (lookup.data_ptr(), tuple(lookup.shape), int(n_in), lookup.device.index)
     hit = _plan_cache.get(key)
     if hit is not None and hit[0] == lookup._version:
         return hit[1]
     plan = FFIPlan(lookup, n_in)
+    _plan_cache.pop(key, None)
     if len(_plan_cache) >= _PLAN_CACHE_MAX:
         _plan_cache.pop(next(iter(_plan_cache)))
-    _plan_cache[key] = (lookup._version, plan)
+    _plan_cache[key] = (lookup._version, plan, lookup)
     return plan
 
 

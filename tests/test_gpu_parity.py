@@ -22,6 +22,16 @@ RTOL = 1e-5
 ATOL = 1e-5
 
 
+def gx_atol(L, K, N):
+    """Absolute floor for grad_x.  grad_x[b,i] sums n = L*K/N products; the rounding error of any
+    fp32 summation grows like sqrt(n) times the size of the partial sums, independently of how
+    close to zero the total lands, so the 1e-5 floor (meant for O(1) sums) is widened by
+    sqrt(n)/32 once n exceeds 1024.  The reference's own fp32 running sum is further from the fp64
+    value than this (checked on the 4,000,000-unit fixture below)."""
+    n = L * K / N
+    return ATOL * max(1.0, n ** 0.5 / 32.0)
+
+
 def run_forward(dev, x, idx, W, transposed, bias=None):
     xin = np.ascontiguousarray(x.T) if transposed else x
     fn = ffi.fan_in_sparse_matmul_tp if transposed else ffi.fan_in_sparse_matmul
@@ -45,7 +55,8 @@ def check_against_oracle(dev, x, idx, W, g, transposed, what=""):
     assert_close(y, oracle.forward_f64(x, idx, W), RTOL, ATOL, what + " y")
     gx, gw = run_backward(dev, x, idx, W, g, transposed)
     assert_close(gw, oracle.grad_w_f64(x, idx, g), RTOL, ATOL, what + " grad_W")
-    assert_close(gx, oracle.grad_x_f64(idx, W, g, N), RTOL, ATOL, what + " grad_x")
+    L, K = idx.shape
+    assert_close(gx, oracle.grad_x_f64(idx, W, g, N), RTOL, gx_atol(L, K, N), what + " grad_x")
     return y, gx, gw
 
 
@@ -81,9 +92,12 @@ def test_reference_fixture_four_million_units(cuda_device):
         gx, gw = run_backward(cuda_device, x, idx, W, g, transposed)
         assert_close(gw, oracle.grad_w_f64(x, idx, g), RTOL, ATOL, "grad_W")
         assert_close(gw.ravel()[::s], gold["grad_w_sample"], RTOL, 1.5e-5, "grad_W vs golden sample")
-        assert_close(gx, oracle.grad_x_f64(idx, W, g, N), RTOL, ATOL, "grad_x")
-        # the reference's own fp32 running sum of 500,000 terms carries ~1e-4 relative error
+        gx64 = oracle.grad_x_f64(idx, W, g, N)
+        assert_close(gx, gx64, RTOL, gx_atol(L, K, N), "grad_x")
+        # the reference's own fp32 running sum of 500,000 terms carries ~1e-4 relative error ...
         assert_close(gx, gold["grad_x"], 5e-4, 1.5e-5, "grad_x vs golden")
+        # ... and is further from the fp64 value than the CUDA result is
+        assert np.abs(gx - gx64).max() <= np.abs(gold["grad_x"] - gx64).max()
 
 
 EXTRA_SHAPES = [
@@ -228,11 +242,13 @@ def test_fused_adam_matches_oracle(cuda_device, n):
     w0 = synth.normal(1, 0, (n,)).numpy()
     w = to_cuda(w0.copy(), dev)
     opt = ffi.FusedAdam([w], lr=1e-3, beta_1=0.9, beta_2=0.999, epsilon=1e-7)
+    # Keras holds the hyper-parameters in the variable's dtype: the oracle gets them rounded to fp32
+    lr, b1, b2, eps = (float(np.float32(v)) for v in (1e-3, 0.9, 0.999, 1e-7))
     wr, mr, vr = w0.astype(np.float64), np.zeros(n), np.zeros(n)
     for step in range(1, 4):
         grad = synth.normal(2, step, (n,)).numpy()
         opt.step([to_cuda(grad, dev)])
-        wr, mr, vr = oracle.adam_f64(wr, mr, vr, grad.astype(np.float64), 1e-3, 0.9, 0.999, 1e-7, step)
+        wr, mr, vr = oracle.adam_f64(wr, mr, vr, grad.astype(np.float64), lr, b1, b2, eps, step)
     assert opt.iterations == 3
     assert_close(w.cpu().numpy(), wr, 1e-5, 1e-6, "adam w")
     assert_close(opt.m[0].cpu().numpy(), mr, 1e-5, 1e-7, "adam m")
@@ -293,14 +309,14 @@ def test_headline_shape_full_size(cuda_device):
     gx, gW = ffi.fan_in_sparse_matmul_grad_tp(xT, idx, W, g)
     y_ref, gx_ref, gW_ref = _torch_reference(xT, idx, W, g)
 
-    def close(a, b, what):
+    def close(a, b, what, atol=ATOL):
         err = (a.double() - b).abs()
-        bound = ATOL + RTOL * b.abs()
+        bound = atol + RTOL * b.abs()
         assert bool((err <= bound).all()), f"{what}: max excess {(err - bound).max().item():.3e}"
 
     close(y, y_ref, "y")
     close(gW, gW_ref, "grad_W")
-    close(gx, gx_ref, "grad_x")
+    close(gx, gx_ref, "grad_x", atol=gx_atol(L, K, N))
     # CPU oracle on a slice of outputs (rows of idx/W are independent for y and grad_W)
     rows = np.r_[0:64, L // 2:L // 2 + 64, L - 64:L]
     x_np = xT.t().contiguous().cpu().numpy()
