@@ -1,0 +1,422 @@
+"""Benchmark of the FFI hot path: forward + backward samples/s of one fixed-fan-in layer.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (`config.workload`): the headline shape B=128, N=768, L=670,091, K=32, fp32, synthetic
+seeded inputs.  One step = forward (with fused bias) + backward (grad_x over the transposed
+index, grad_W, grad_bias) of the layer, through the op "FanInSparseMatmulTp" and its gradient.
+With N > 1 ranks the L outputs are split evenly over the ranks, x is replicated and the [N,B]
+grad_x partials are all-reduced with NCCL (strong scaling: the total work is fixed).
+
+Prints ONE JSON line on rank 0.  `value` is samples/s with inputs resident in HBM; `e2e` is the
+same step driven from HOST buffers (x and sparse targets copied from pinned memory, logits ->
+fused sigmoid-BCE gradient on the device, loss and grad_x copied back), all inside the timed
+region.  `roofline` describes the slowest kernel of the step; `cpu_baseline` / `--impl reference`
+time the reference's own CPU kernels on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HEADLINE = dict(B=128, N=768, L=670_091, K=32)
+CPU_SAMPLE_DIVISOR = 16          # the CPU arms time L/16 of the outputs per step
+SEED = 2023
+FMA_PER_CLK_PER_SM = 128
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
+# profiles/ (None until a capture of that kernel exists).
+NCU_TRAFFIC_BYTES = {"forward": None, "grad_w": None, "grad_x": None}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=HEADLINE["B"])
+    ap.add_argument("--units", type=int, default=HEADLINE["L"])
+    ap.add_argument("--n-in", type=int, default=HEADLINE["N"])
+    ap.add_argument("--fan-in", type=int, default=HEADLINE["K"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured", float(d.get("sm_max_mhz", 1965.0))
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback", 1965.0
+
+
+def algorithmic_bytes(B, N, L, K):
+    """Compulsory HBM bytes per pass (fp32 x and W, int32 idx, fp32 y / g / gradients)."""
+    return {
+        "forward": L * K * 8 + 4 * L + B * N * 4 + 4 * B * L,
+        "grad_w": 4 * B * L + 4 * L * K + B * N * 4 + 4 * L * K + 4 * L,
+        "grad_x": 4 * B * L + L * K * 8 + 4 * B * N,
+    }
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and clock-event reasons of one GPU through NVML while the benchmark runs."""
+
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+        0x80: "hw_power_brake", 0x2: "applications_clocks_setting", 0x100: "display_clock_setting",
+        0x10: "sync_boost",
+    }
+
+    def __init__(self, index: int, period: float = 0.01):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples = []  # (time, sm_mhz, reasons bitmask)
+        self.max_mhz = None
+        self.stop_flag = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if visible:
+                ids = [v for v in visible.split(",") if v != ""]
+                if index < len(ids) and ids[index].isdigit():
+                    phys = int(ids[index])
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        while not self.stop_flag.is_set():
+            try:
+                mhz = int(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                try:
+                    reasons = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                except Exception:
+                    reasons = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                self.samples.append((time.time(), mhz, reasons))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def summary(self, t0: float, t1: float):
+        if not self.ok:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable"]}
+        window = [s for s in self.samples if t0 <= s[0] <= t1]
+        if len(window) < 3:
+            window = self.samples
+        mask = 0
+        for _, _, r in window:
+            mask |= r
+        names = [n for bit, n in self.REASONS.items() if mask & bit]
+        return {"sm_mhz": statistics.median(s[1] for s in window) if window else None, "sm_max_mhz": self.max_mhz,
+                "reasons": names, "samples": len(window)}
+
+
+# --------------------------------------------------------------------------- reference arm
+
+def cpu_step_inputs(B, N, L, K, L_sample):
+    """Host copies of the first L_sample output rows of the benchmark's seeded inputs."""
+    from ecml23_sparse_b200 import synth
+
+    x = synth.normal(SEED, 0, (N, B)).numpy()  # [N,B]: the transposed op, as the layer calls it
+    idx = synth.indices_without_replacement(SEED, 1, L_sample, K, N).numpy()
+    W = synth.normal(SEED, 2, (L_sample, K), std=(1.0 / K) ** 0.5).numpy()
+    g = synth.normal(SEED, 3, (B, L_sample)).numpy()
+    return x, idx, W, g
+
+
+def time_cpu_reference(B, N, L, K, steps, warmup, budget_s=25.0):
+    """samples/s of the reference's CPU kernels (all host threads) on L/16 of the outputs per step,
+    scaled to the full L (the CPU work is linear in L).  Falls back to the C port of those kernels
+    when the compiled reference is not present."""
+    import oracle
+
+    L_sample = max(1, L // CPU_SAMPLE_DIVISOR)
+    x, idx, W, g = cpu_step_inputs(B, N, L, K, L_sample)
+    use_ref = oracle.ref_available()
+    threads = oracle.ref_lib().ref_hardware_threads() if use_ref else oracle.max_threads()
+
+    def step():
+        if use_ref:
+            oracle.ref_forward(x, idx, W, transposed=True, threads=0)
+            oracle.ref_backward(x, idx, W, g, transposed=True, threads=0)
+        else:
+            oracle.forward_f32(x, idx, W, transposed=True, threads=0)
+            oracle.grad_w_f32(x, idx, g, transposed=True, threads=0)
+            oracle.grad_x_f32(idx, W, g, N, transposed=True, threads=0)
+
+    t_start = time.perf_counter()
+    for _ in range(warmup):
+        step()
+        if time.perf_counter() - t_start > budget_s / 3:
+            break
+    times = []
+    t_start = time.perf_counter()
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_start > budget_s:
+            break
+    per_step = statistics.median(times) * (L / L_sample)
+    return {
+        "value": B / per_step,
+        "unit": "samples/s",
+        "cores": int(threads),
+        "kind": "reference" if use_ref else "port",
+        "sample": f"first {L_sample} of {L} outputs per step (1/{CPU_SAMPLE_DIVISOR}), full batch, "
+                  f"{len(times)} steps, time scaled by {L / L_sample:.2f}",
+        "ms_per_step_full": per_step * 1e3,
+    }
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    B, N, L, K = args.batch, args.n_in, args.units, args.fan_in
+    cb = time_cpu_reference(B, N, L, K, args.steps, args.warmup, budget_s=120.0)
+    line = {
+        "impl": "reference",
+        "metric": "FFI fwd+bwd samples/sec", "value": cb["value"], "unit": "samples/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": cb["ms_per_step_full"], "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(B, N, L, K, args.gpus),
+        "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": cb["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(B, N, L, K, gpus):
+    return {
+        "workload": f"single FFI layer fwd+bwd, B={B}, N={N}, L={L}, K={K}, fp32 (op FanInSparseMatmulTp + grad)",
+        "B": B, "N": N, "L": L, "K": K,
+        "parallelism": f"label-sharded x{gpus}" if gpus > 1 else "single GPU",
+        "l2": "256 MiB buffer rewritten between timed steps (L2 flush); per-step CUDA events",
+    }
+
+
+# --------------------------------------------------------------------------------- our arm
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import ecml23_sparse_b200 as ffi
+    from ecml23_sparse_b200 import ops, sharded, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py --impl ours needs a CUDA device: the FFI kernels have no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, N, L, K = args.batch, args.n_in, args.units, args.fan_in
+    lo, hi = sharded.shard_range(L, world, rank)
+    Ls = hi - lo
+
+    # ---- inputs resident in HBM -----------------------------------------------------------
+    xT = synth.normal(SEED, 0, (N, B), device=dev)
+    idx = synth.indices_without_replacement(SEED, 1, Ls, K, N, device=dev, row_offset=lo)
+    W = synth.normal(SEED, 2, (Ls, K), std=(1.0 / K) ** 0.5, device=dev, start=lo * K)
+    bias = torch.zeros(Ls, device=dev)
+    g = synth.normal(SEED, 3 + 16 * rank, (B, Ls), device=dev)  # upstream gradient of this shard
+    plan = ffi.FFIPlan(idx, N)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step_resident():
+        y = ops._forward(xT, idx, W, bias, True)
+        gx, gW, gb = ops._backward(xT, idx, W, g, True, plan=plan, want_bias_grad=True)
+        if world > 1:
+            dist.all_reduce(gx)
+        return y, gx, gW, gb
+
+    nbt_gw = 1 if B <= 32 else (B + 63) // 64  # grad_W runs one launch per batch tile of 64 at N=768
+    launches_per_step = 1 + nbt_gw + 2           # forward, grad_W tiles, grad_x + its partial reduce
+
+    def timed_loop(fn, steps, warmup):
+        for _ in range(warmup):
+            flush.fill_(1)
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        events = []
+        t0 = time.time()
+        for _ in range(steps):
+            flush.fill_(1)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            events.append((s, e))
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t1 = time.time()
+        total_ms = sum(s.elapsed_time(e) for s, e in events)
+        t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), t0, t1
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+
+    total_ms, t0, t1 = timed_loop(step_resident, args.steps, max(3, args.warmup))
+    ms_per_step = total_ms / args.steps
+    value = B / (ms_per_step * 1e-3)
+
+    # ---- end to end from host buffers -----------------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        x_host = synth.normal(SEED, 0, (N, B)).t().contiguous().pin_memory()          # [B,N] on the host
+        rp_host, lab_host = synth.multi_hot_targets(SEED, 5, B, L)
+        rp_host, lab_host = rp_host.pin_memory(), lab_host.pin_memory()
+        x_dev = torch.empty((B, N), device=dev)
+        rp_dev = torch.empty_like(rp_host, device=dev)
+        lab_dev = torch.empty_like(lab_host, device=dev)
+        gx_host = torch.empty((B, N)).pin_memory()
+        loss_host = torch.empty(()).pin_memory()
+
+        def step_e2e():
+            x_dev.copy_(x_host, non_blocking=True)
+            rp_dev.copy_(rp_host, non_blocking=True)
+            lab_dev.copy_(lab_host, non_blocking=True)
+            y = ops._forward(x_dev, idx, W, bias, False)
+            loss, gz = ffi.sparse_bce_with_logits(y, rp_dev, lab_dev, total_labels=L, label_offset=lo, inplace=True)
+            gx, gW, gb = ops._backward(x_dev, idx, W, gz, False, plan=plan, want_bias_grad=True)
+            if world > 1:
+                dist.all_reduce(gx)
+                dist.all_reduce(loss)
+            gx_host.copy_(gx, non_blocking=True)
+            loss_host.copy_(loss, non_blocking=True)
+
+        e2e_ms, _, _ = timed_loop(step_e2e, args.steps, max(3, args.warmup))
+        e2e = {
+            "value": B / (e2e_ms / args.steps * 1e-3), "unit": "samples/s",
+            "h2d_bytes_per_step": int(x_host.numel() * 4 + rp_host.numel() * 4 + lab_host.numel() * 4),
+            "d2h_bytes_per_step": int(gx_host.numel() * 4 + 4),
+            "ms_per_step": e2e_ms / args.steps,
+            "path": "pinned host x[B,N] + CSR targets -> FanInSparseMatmul(+bias) -> sigmoid-BCE grad -> "
+                    "FanInSparseMatmulGrad -> loss and grad_x to host",
+        }
+
+    # ---- per-kernel times for the roofline (rank-local, each call timed alone) -------------
+    def time_call(fn, reps=20):
+        for _ in range(3):
+            flush.fill_(1)
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            flush.fill_(1)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            e.synchronize()
+            ts.append(s.elapsed_time(e))
+        return sum(ts) / len(ts)
+
+    kernel_ms = {
+        "forward": time_call(lambda: ops._forward(xT, idx, W, bias, True)),
+        "grad_w": time_call(lambda: ops._backward(xT, idx, W, g, True, plan=plan, want_feature_grad=False,
+                                                  want_bias_grad=True)),
+        "grad_x": time_call(lambda: ops._backward(xT, idx, W, g, True, plan=plan, want_weight_grad=False)),
+    }
+    sampler.stop_flag.set()
+    sampler.join(timeout=2)
+    clocks = sampler.summary(t0, t1)
+
+    hbm_gbs, peak_kind, sm_max_mhz = measured_peaks()
+    alg = algorithmic_bytes(B, N, Ls, K)
+    sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
+    fma_peak = sm_count * FMA_PER_CLK_PER_SM * sm_max_mhz * 1e6
+    kernels = {}
+    for name, ms in kernel_ms.items():
+        launches = nbt_gw if name == "grad_w" else 1
+        t_hbm = alg[name] / (hbm_gbs * 1e9)
+        t_fma = B * Ls * K / fma_peak
+        kernels[name] = {
+            "ms": ms, "launches": launches, "algorithmic_bytes": alg[name], "achieved_gbs": alg[name] / (ms * 1e-3) / 1e9,
+            "frac_of_hbm_peak": alg[name] / (ms * 1e-3) / 1e9 / hbm_gbs,
+            "frac_of_max_hbm_fma_roofline": max(t_hbm, t_fma) / (ms * 1e-3),
+            "fma_per_s": B * Ls * K / (ms * 1e-3),
+        }
+    dominant = max(kernel_ms, key=kernel_ms.get)
+    dk = kernels[dominant]
+    roofline = {
+        "kernel": {"forward": "ffi_fwd_kernel", "grad_w": "ffi_grad_w_kernel", "grad_x": "ffi_grad_x_narrow_kernel"}[dominant],
+        "bound": "hbm", "achieved": dk["achieved_gbs"], "peak": hbm_gbs, "unit": "GB/s",
+        "frac": dk["achieved_gbs"] / hbm_gbs, "peak_kind": f"of {peak_kind}",
+        "traffic": NCU_TRAFFIC_BYTES.get(dominant),
+        "algorithmic_bytes_per_launch": dk["algorithmic_bytes"] / dk["launches"],
+        "avg_launch_ms": dk["ms"] / dk["launches"],
+        "step_frac_of_roofline": sum(max(alg[k] / (hbm_gbs * 1e9), B * Ls * K / fma_peak) for k in alg) /
+                                 (sum(kernel_ms.values()) * 1e-3),
+        "kernels": kernels,
+    }
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cb = time_cpu_reference(B, N, L, K, steps=8, warmup=1, budget_s=20.0)
+        cpu_baseline = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    if rank == 0:
+        line = {
+            "metric": "FFI fwd+bwd samples/sec", "value": value, "unit": "samples/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": workload_config(B, N, L, K, world),
+            "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+            "roofline": roofline, "cpu_baseline": cpu_baseline,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

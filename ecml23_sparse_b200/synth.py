@@ -52,11 +52,12 @@ def uniform_pm1(seed: int, stream: int, shape, device="cpu") -> torch.Tensor:
     return (u * 2 - 1).reshape(shape)
 
 
-def normal(seed: int, stream: int, shape, std: float = 1.0, device="cpu") -> torch.Tensor:
-    """float32 N(0, std^2) by Box-Muller."""
+def normal(seed: int, stream: int, shape, std: float = 1.0, device="cpu", start: int = 0) -> torch.Tensor:
+    """float32 N(0, std^2) by Box-Muller; `start` offsets the counter (to draw a slice of a larger
+    tensor: element j of the slice is element start+j of the whole)."""
     n = math.prod(shape)
-    u1 = uniform01(seed, stream, n, device)
-    u2 = uniform01(seed, stream + 1_000_003, n, device)
+    u1 = uniform01(seed, stream, n, device, start)
+    u2 = uniform01(seed, stream + 1_000_003, n, device, start)
     z = torch.sqrt(-2.0 * torch.log(u1)) * torch.cos(2.0 * math.pi * u2)
     return (z * std).to(torch.float32).reshape(shape)
 
@@ -69,16 +70,17 @@ def indices_with_replacement(seed: int, stream: int, L: int, K: int, N: int, dev
 
 
 def indices_without_replacement(seed: int, stream: int, L: int, K: int, N: int, device="cpu",
-                                rows_per_block: int = 32768) -> torch.Tensor:
+                                rows_per_block: int = 32768, row_offset: int = 0) -> torch.Tensor:
     """int32 [L,K]: per row, K distinct inputs drawn uniformly from [0,N) (the K smallest of N
-    random keys, listed in key order)."""
+    random keys, listed in key order).  Row r of the result is row row_offset+r of the full table."""
     if K > N:
         raise ValueError("K distinct indices need K <= N")
     out = torch.empty((L, K), dtype=torch.int32, device=device)
     col = torch.arange(N, dtype=torch.int64, device=device)
     for r0 in range(0, L, rows_per_block):
         r1 = min(L, r0 + rows_per_block)
-        ctr = (torch.arange(r0, r1, dtype=torch.int64, device=device)[:, None] * N + col[None, :])
+        ctr = (torch.arange(row_offset + r0, row_offset + r1, dtype=torch.int64, device=device)[:, None] * N
+               + col[None, :])
         keys = (_lsr(hash64(seed, stream, ctr), 12) << 20) | col[None, :]  # unique within a row
         sel = torch.topk(keys, K, dim=1, largest=False, sorted=True).values
         out[r0:r1] = (sel & ((1 << 20) - 1)).to(torch.int32)
