@@ -63,6 +63,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_kernel(FwdKernelParams p)
     if (XSMEM) {
         // x_s[i][lane*BPL + j] holds batch element b0 + lane + 32*j.
         const int total = p.N * BT;
+#pragma unroll 8
         for (int e = tid; e < total; e += kThreads) {
             int i = e / BT;
             int bl = e - i * BT;
@@ -102,69 +103,84 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_kernel(FwdKernelParams p)
     const V* xg_lane = reinterpret_cast<const V*>(p.xT + b0) + lane;
     const size_t ldv = static_cast<size_t>(p.ldx / BPL);
 
-    int t = blockIdx.x;
-    int buf = 0;
-    if (t < p.numTiles) prefetch(t, 0);
-    for (; t < p.numTiles; t += gridDim.x, buf ^= 1) {
-        __pipeline_wait_prior(0);
-        __syncthreads();  // tile t landed; y_s and the other tile buffer are free again
-        const int tn = t + gridDim.x;
-        if (tn < p.numTiles) prefetch(tn, buf ^ 1);
-
-        const long long o0 = static_cast<long long>(t) * TO;
-        const float* wb = w_s + buf * tileElems;
-        const int* ib = i_s + buf * tileElems;
-        for (int ol = warp; ol < TO; ol += kWarps) {
-            const long long o = o0 + ol;
-            if (o >= L) break;
-            const float bias = p.bias ? __ldg(p.bias + o) : 0.f;
-            float acc[BPL];
-#pragma unroll
-            for (int j = 0; j < BPL; ++j) acc[j] = bias;
-            const int4* ir = reinterpret_cast<const int4*>(ib + ol * Kp);
-            const float4* wr = reinterpret_cast<const float4*>(wb + ol * Kp);
-#pragma unroll 2
-            for (int k4 = 0; k4 < Kp / 4; ++k4) {
-                const int4 ii = ir[k4];
-                const float4 ww = wr[k4];
-                V v0, v1, v2, v3;
-                if (XSMEM) {
-                    v0 = xs_lane[ii.x * 32];
-                    v1 = xs_lane[ii.y * 32];
-                    v2 = xs_lane[ii.z * 32];
-                    v3 = xs_lane[ii.w * 32];
-                } else {
-                    v0 = __ldg(xg_lane + ii.x * ldv);
-                    v1 = __ldg(xg_lane + ii.y * ldv);
-                    v2 = __ldg(xg_lane + ii.z * ldv);
-                    v3 = __ldg(xg_lane + ii.w * ldv);
-                }
-#pragma unroll
-                for (int j = 0; j < BPL; ++j) {
-                    acc[j] = fmaf(ww.x, vec_get(v0, j), acc[j]);
-                    acc[j] = fmaf(ww.y, vec_get(v1, j), acc[j]);
-                    acc[j] = fmaf(ww.z, vec_get(v2, j), acc[j]);
-                    acc[j] = fmaf(ww.w, vec_get(v3, j), acc[j]);
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < BPL; ++j) {
-                const int bl = XSMEM ? lane + 32 * j : lane * BPL + j;
-                y_s[ol * (BT + 1) + bl] = acc[j];
-            }
-        }
-        __syncthreads();  // y_s complete
-
-        // Coalesced write-out: one warp per batch row, lanes along o.
+    // Coalesced write-out of a finished tile: one warp per batch row, lanes along o.
+    auto write_out = [&](long long o0, const float* ys) {
         for (int r = warp; r < BT; r += kWarps) {
             const int b = b0 + r;
             if (b >= p.B) break;
             float* yrow = p.y + static_cast<size_t>(b) * L + o0;
             for (int c = lane; c < TO; c += 32)
-                if (o0 + c < L) yrow[c] = y_s[c * (BT + 1) + r];
+                if (o0 + c < L) yrow[c] = ys[c * (BT + 1) + r];
         }
+    };
+
+    auto gather = [&](int i) -> V {
+        if (XSMEM) return xs_lane[i * 32];
+        return __ldg(xg_lane + i * ldv);
+    };
+
+    int t = blockIdx.x;
+    int buf = 0;
+    long long prev_o0 = -1;  // tile whose results wait in y_s[buf ^ 1]
+    if (t < p.numTiles) prefetch(t, 0);
+    for (; t < p.numTiles; t += gridDim.x, buf ^= 1) {
+        __pipeline_wait_prior(0);
+        // One barrier per tile: tile t has landed, every warp has finished computing tile t-1
+        // (so y_s[buf^1] is complete and the other W/idx buffer is free) and writing out t-2.
+        __syncthreads();
+        const int tn = t + gridDim.x;
+        if (tn < p.numTiles) prefetch(tn, buf ^ 1);
+        if (prev_o0 >= 0) write_out(prev_o0, y_s + (buf ^ 1) * TO * (BT + 1));
+
+        const long long o0 = static_cast<long long>(t) * TO;
+        const float* wb = w_s + buf * tileElems;
+        const int* ib = i_s + buf * tileElems;
+        float* ys = y_s + buf * TO * (BT + 1);
+        // Two rows per warp in flight: twice the independent loads and FMA chains per warp.
+        for (int olA = warp; olA < TO; olA += 2 * kWarps) {
+            if (o0 + olA >= L) break;
+            const int olB = olA + kWarps;
+            const bool validB = olB < TO && o0 + olB < L;
+            const int olBc = validB ? olB : olA;
+            const float biasA = p.bias ? __ldg(p.bias + o0 + olA) : 0.f;
+            const float biasB = p.bias ? __ldg(p.bias + o0 + olBc) : 0.f;
+            float accA[BPL], accB[BPL];
+#pragma unroll
+            for (int j = 0; j < BPL; ++j) accA[j] = accB[j] = 0.f;  // bias is added last
+            const int4* irA = reinterpret_cast<const int4*>(ib + olA * Kp);
+            const float4* wrA = reinterpret_cast<const float4*>(wb + olA * Kp);
+            const int4* irB = reinterpret_cast<const int4*>(ib + olBc * Kp);
+            const float4* wrB = reinterpret_cast<const float4*>(wb + olBc * Kp);
+#pragma unroll 2
+            for (int k4 = 0; k4 < Kp / 4; ++k4) {
+                const int4 iA = irA[k4], iB = irB[k4];
+                const float4 wA = wrA[k4], wB = wrB[k4];
+                const V a0 = gather(iA.x), a1 = gather(iA.y), a2 = gather(iA.z), a3 = gather(iA.w);
+                const V c0 = gather(iB.x), c1 = gather(iB.y), c2 = gather(iB.z), c3 = gather(iB.w);
+#pragma unroll
+                for (int j = 0; j < BPL; ++j) {
+                    accA[j] = fmaf(wA.x, vec_get(a0, j), accA[j]);
+                    accB[j] = fmaf(wB.x, vec_get(c0, j), accB[j]);
+                    accA[j] = fmaf(wA.y, vec_get(a1, j), accA[j]);
+                    accB[j] = fmaf(wB.y, vec_get(c1, j), accB[j]);
+                    accA[j] = fmaf(wA.z, vec_get(a2, j), accA[j]);
+                    accB[j] = fmaf(wB.z, vec_get(c2, j), accB[j]);
+                    accA[j] = fmaf(wA.w, vec_get(a3, j), accA[j]);
+                    accB[j] = fmaf(wB.w, vec_get(c3, j), accB[j]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < BPL; ++j) {
+                const int bl = XSMEM ? lane + 32 * j : lane * BPL + j;
+                ys[olA * (BT + 1) + bl] = accA[j] + biasA;
+                if (validB) ys[olB * (BT + 1) + bl] = accB[j] + biasB;
+            }
+        }
+        prev_o0 = o0;
     }
     __pipeline_wait_prior(0);
+    __syncthreads();
+    if (prev_o0 >= 0) write_out(prev_o0, y_s + (buf ^ 1) * TO * (BT + 1));
 }
 
 __global__ void transpose_pad_kernel(const float* __restrict__ src, float* __restrict__ dst,
@@ -193,14 +209,14 @@ struct FwdConfig {
 size_t fwd_smem_bytes(int N, int bpl, bool xsmem, int TO, int Kp) {
     const size_t BT = 32 * bpl;
     return (xsmem ? static_cast<size_t>(N) * BT * 4 : 0) + static_cast<size_t>(2) * TO * Kp * 8 +
-           static_cast<size_t>(TO) * (BT + 1) * 4;
+           static_cast<size_t>(2) * TO * (BT + 1) * 4;
 }
 
 int pick_TO(size_t budget, int N, int bpl, bool xsmem, int Kp) {
     const size_t BT = 32 * bpl;
     const size_t fixed = xsmem ? static_cast<size_t>(N) * BT * 4 : 0;
     if (fixed >= budget) return 0;
-    const size_t per_row = static_cast<size_t>(2) * Kp * 8 + (BT + 1) * 4;
+    const size_t per_row = static_cast<size_t>(2) * Kp * 8 + 2 * (BT + 1) * 4;
     size_t to = (budget - fixed) / per_row;
     if (to > 128) to = 128;
     return static_cast<int>(to / 16 * 16);

@@ -21,6 +21,7 @@ namespace {
 
 constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
+constexpr int kGRegs = 8;  // registers per thread that stage the next g tile
 
 struct GradWKernelParams {
     const float* xT;
@@ -80,6 +81,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_grad_w_kernel(GradWKernelPara
     for (int e = tid; e < 2 * tileElems; e += kThreads) i_s[e] = 0;
     if (XSMEM) {
         const int total = p.N * BT;
+#pragma unroll 8
         for (int e = tid; e < total; e += kThreads) {
             int i = e / BT;
             int bl = e - i * BT;
@@ -113,23 +115,43 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_grad_w_kernel(GradWKernelPara
     const V* xg_lane = reinterpret_cast<const V*>(p.xT + b0) + lane;
     const size_t ldv = static_cast<size_t>(p.ldx / BPL);
 
+    // The g tile of the next output tile is fetched into registers while the current tile is
+    // being computed (kGRegs * 512 >= TO * BT by construction of TO).
+    float gpre[kGRegs];
+    auto load_g = [&](int t) {
+        const long long o0 = static_cast<long long>(t) * TO;
+#pragma unroll
+        for (int u = 0; u < kGRegs; ++u) {
+            const int e = tid + u * kThreads;
+            const int r = e / TO, c = e - r * TO;
+            const int b = b0 + r;
+            gpre[u] = (r < BT && b < p.B && o0 + c < L) ? __ldg(p.g + static_cast<size_t>(b) * L + o0 + c) : 0.f;
+        }
+    };
+
     int t = blockIdx.x;
     int buf = 0;
-    if (t < p.numTiles) prefetch(t, 0);
+    if (t < p.numTiles) {
+        prefetch(t, 0);
+        load_g(t);
+    }
     for (; t < p.numTiles; t += gridDim.x, buf ^= 1) {
         const long long o0 = static_cast<long long>(t) * TO;
         __syncthreads();  // everyone is done reading g_s of the previous tile
         // g tile, transposed into g_s[o][b] (row stride BT+1: conflict-free both ways).
-        for (int r = warp; r < BT; r += kWarps) {
-            const int b = b0 + r;
-            const float* grow = p.g + static_cast<size_t>(b) * L + o0;
-            for (int c = lane; c < TO; c += 32)
-                g_s[c * (BT + 1) + r] = (b < p.B && o0 + c < L) ? __ldg(grow + c) : 0.f;
+#pragma unroll
+        for (int u = 0; u < kGRegs; ++u) {
+            const int e = tid + u * kThreads;
+            const int r = e / TO, c = e - r * TO;
+            if (r < BT) g_s[c * (BT + 1) + r] = gpre[u];
         }
         __pipeline_wait_prior(0);
         __syncthreads();  // idx tile t and g_s visible
         const int tn = t + gridDim.x;
-        if (tn < p.numTiles) prefetch(tn, buf ^ 1);
+        if (tn < p.numTiles) {
+            prefetch(tn, buf ^ 1);
+            load_g(tn);
+        }
 
         const int* ib = i_s + buf * tileElems;
         for (int ol = warp; ol < TO; ol += kWarps) {
@@ -209,6 +231,7 @@ int gw_pick_TO(size_t budget, int N, int bpl, bool xsmem, int Kp) {
     const size_t per_row = static_cast<size_t>(2) * Kp * 4 + (BT + 1) * 4;
     size_t to = (budget - fixed) / per_row;
     if (to > 128) to = 128;
+    if (to * BT > static_cast<size_t>(kGRegs) * kThreads) to = kGRegs * kThreads / BT;
     return static_cast<int>(to / 16 * 16);
 }
 

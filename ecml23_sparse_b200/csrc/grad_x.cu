@@ -29,6 +29,13 @@ namespace {
 constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
 
+template <int BPL>
+__device__ __forceinline__ void store_vec(float* dst, const float (&v)[BPL]) {
+    if constexpr (BPL == 4) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+    else if constexpr (BPL == 2) *reinterpret_cast<float2*>(dst) = make_float2(v[0], v[1]);
+    else *dst = v[0];
+}
+
 struct GxNarrowParams {
     const float* W;
     const float* g;
@@ -79,25 +86,35 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_grad_x_narrow_kernel(GxNarrow
 
         // (1) g tile.  Work item u = (row group of 8, granule, slot, row in group): a warp
         // covers 8 consecutive rows x BPL slots of one granule -> 32 distinct banks.
+        // Item u = (granule gl, row ol): BPL coalesced 4-byte loads (lanes run along o), one
+        // vector store of the granule.  Four items are in flight per thread.
         {
-            constexpr int ROWS_PER_WARP_ITEM = 32 / GR;  // rows covered by one warp-wide copy
-            const int itemsPerGranule = (T + ROWS_PER_WARP_ITEM - 1) / ROWS_PER_WARP_ITEM;
-            const int totalItems = itemsPerGranule * 32;  // x 32 granules
-            for (int it = warp; it < totalItems; it += kWarps) {
-                const int gl = it & 31;                    // logical granule (= lane that will read it)
-                const int rg = it >> 5;                    // row group
-                const int ol = rg * ROWS_PER_WARP_ITEM + lane / GR;
-                const int q = lane % GR;                   // slot inside the granule
-                const int b = b0 + gl * GR + q;
-                if (ol < T) {
-                    float* dst = g_s + static_cast<size_t>(ol) * BT + ((gl ^ (ol & SW)) * GR) + q;
-                    if (ol < nrows && b < p.B)
-                        __pipeline_memcpy_async(dst, p.g + static_cast<size_t>(b) * L + o0 + ol, 4);
-                    else
-                        *dst = 0.f;
+            const int totalItems = T * 32;
+            constexpr int kBatch = 4;
+            for (int u0 = tid; u0 < totalItems; u0 += kThreads * kBatch) {
+                float v[kBatch][BPL];
+#pragma unroll
+                for (int k = 0; k < kBatch; ++k) {
+                    const int u = u0 + k * kThreads;
+                    const int gl = u / T, ol = u - gl * T;
+#pragma unroll
+                    for (int q = 0; q < BPL; ++q) {
+                        const int b = b0 + gl * GR + q;
+                        v[k][q] = (u < totalItems && ol < nrows && b < p.B)
+                                      ? __ldg(p.g + static_cast<size_t>(b) * L + o0 + ol)
+                                      : 0.f;
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < kBatch; ++k) {
+                    const int u = u0 + k * kThreads;
+                    const int gl = u / T, ol = u - gl * T;
+                    if (u < totalItems) {
+                        float* dst = g_s + static_cast<size_t>(ol) * BT + ((gl ^ (ol & SW)) * GR);
+                        store_vec<BPL>(dst, v[k]);
+                    }
                 }
             }
-            __pipeline_commit();
         }
 
         // (2) run offsets of my input slice and the staged entries.
