@@ -163,6 +163,9 @@ extern "C" size_t ffi_backward_workspace_bytes(const ffi_plan* plan, int64_t B, 
         total += plan_x(smem, B, N, x_transposed).bytes;
     }
     if (want_grad_x && plan) total += align_up(grad_x_workspace_bytes(plan, B));
+    // the transposed upstream gradient gT[L][ldg], shared by grad_x and the barrier-free grad_W kernel
+    if (want_grad_x || (want_grad_w && K % 4 == 0))
+        total += align_up(static_cast<size_t>(L) * transposed_g_stride(B) * 4);
     return total;
 }
 
@@ -187,6 +190,22 @@ extern "C" int ffi_backward(const void* x, const int32_t* idx, const void* W, co
     if (workspace && reinterpret_cast<uintptr_t>(workspace) % kAlign != 0)
         return fail(FFI_ERR_WORKSPACE, "workspace must be %zu-byte aligned", kAlign);
 
+    // g transposed to [L][ldg] once, for the kernels that read whole batch rows of g.
+    const bool gw_stream = (grad_w || grad_bias) &&
+                           grad_w_stream_applicable(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), idx);
+    const float* gT = nullptr;
+    const int64_t ldg = transposed_g_stride(B);
+    if (grad_x || gw_stream) {
+        const size_t bytes = align_up(static_cast<size_t>(L) * ldg * 4);
+        if (!workspace || workspace_bytes < used + bytes)
+            return fail(FFI_ERR_WORKSPACE, "ffi_backward needs %zu bytes of workspace for the transposed gradient", bytes);
+        float* dst = reinterpret_cast<float*>(ws + used);
+        rc = launch_transpose_g(g, dst, static_cast<int>(B), L, ldg, stream);
+        if (rc != FFI_OK) return rc;
+        gT = dst;
+        used += bytes;
+    }
+
     if (grad_w || grad_bias) {
         const bool smem = grad_w_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
         const XPlan xp = plan_x(smem, B, N, x_transposed);
@@ -202,6 +221,8 @@ extern "C" int ffi_backward(const void* x, const int32_t* idx, const void* W, co
         a.ldx = xp.ld;
         a.idx = idx;
         a.g = g;
+        a.gT = gT;
+        a.ldg = ldg;
         a.gW = grad_w;
         a.gbias = grad_bias;
         a.B = static_cast<int>(B);
@@ -216,6 +237,8 @@ extern "C" int ffi_backward(const void* x, const int32_t* idx, const void* W, co
         a.idx = idx;
         a.W = static_cast<const float*>(W);
         a.g = g;
+        a.gT = gT;
+        a.ldg = ldg;
         a.plan = plan;
         a.gx = grad_x;
         a.x_transposed = x_transposed;

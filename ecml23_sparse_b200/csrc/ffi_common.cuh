@@ -83,11 +83,20 @@ struct GradWArgs {
     int64_t ldx;
     const int32_t* idx;
     const float* g;
+    const float* gT;  // g transposed to [L][ldg] (batch contiguous, zero padded), or nullptr
+    int64_t ldg;
     float* gW;
     float* gbias;
     int B, N, L, K;
 };
 int launch_grad_w(const GradWArgs& a, cudaStream_t stream);
+// True when launch_grad_w will take the barrier-free kernel, which reads gT instead of g.
+bool grad_w_stream_applicable(int B, int N, int K, const void* idx);
+
+// Row stride of the transposed upstream gradient gT[L][ldg] for a batch of B.
+int64_t transposed_g_stride(int64_t B);
+// g [B][L] -> gT [L][ldg], zero padded in the batch dimension.
+int launch_transpose_g(const float* g, float* gT, int B, int64_t L, int64_t ldg, cudaStream_t stream);
 
 // x [B,N] -> xT [N][ldx] (zero padded to ldx), fp32.
 int launch_transpose_pad(const float* src, float* dst, int rows, int cols, int64_t ld_dst,
@@ -115,6 +124,8 @@ struct GradXArgs {
     const int32_t* idx;
     const float* W;
     const float* g;
+    const float* gT;  // as in GradWArgs; required by the narrow-input kernel
+    int64_t ldg;
     const ffi_plan* plan;
     float* gx;
     int x_transposed;  // layout of gx: [N,B] if set, else [B,N]
@@ -123,6 +134,8 @@ struct GradXArgs {
     size_t workspace_bytes;
 };
 size_t grad_x_workspace_bytes(const ffi_plan* plan, int64_t B);
+// True when launch_grad_x will take the register-accumulator kernel, which reads gT.
+bool grad_x_narrow_applicable(const ffi_plan* plan, int64_t B);
 int launch_grad_x(const GradXArgs& a, cudaStream_t stream);
 
 }  // namespace ffi

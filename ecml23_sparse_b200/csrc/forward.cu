@@ -258,10 +258,18 @@ bool forward_uses_smem_x(int B, int N, int K, int* bpl_out) {
     return false;
 }
 
+int launch_forward_stream(const FwdArgs& a, cudaStream_t stream, bool* handled);
+
 int launch_forward(const FwdArgs& a, cudaStream_t stream) {
     DeviceInfo dev;
     int rc = get_device_info(&dev);
     if (rc != FFI_OK) return rc;
+    {
+        // Preferred: the barrier-free kernel (x tile in shared memory, K % 4 == 0, aligned rows).
+        bool handled = false;
+        rc = launch_forward_stream(a, stream, &handled);
+        if (rc != FFI_OK || handled) return rc;
+    }
 
     FwdKernelParams p;
     p.xT = a.xT;

@@ -297,10 +297,18 @@ bool grad_w_uses_smem_x(int B, int N, int K, int* bpl_out) {
     return false;
 }
 
+int launch_grad_w_stream(const GradWArgs& a, cudaStream_t stream, bool* handled);
+
 int launch_grad_w(const GradWArgs& a, cudaStream_t stream) {
     DeviceInfo dev;
     int rc = get_device_info(&dev);
     if (rc != FFI_OK) return rc;
+    {
+        // Preferred: the barrier-free kernel (x tile in shared memory, K % 4 == 0, aligned idx).
+        bool handled = false;
+        rc = launch_grad_w_stream(a, stream, &handled);
+        if (rc != FFI_OK || handled) return rc;
+    }
 
     GradWKernelParams p;
     p.xT = a.xT;

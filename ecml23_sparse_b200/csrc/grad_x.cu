@@ -38,7 +38,8 @@ __device__ __forceinline__ void store_vec(float* dst, const float (&v)[BPL]) {
 
 struct GxNarrowParams {
     const float* W;
-    const float* g;
+    const float* gT;  // upstream gradient transposed to [L][ldg], zero padded batch
+    long long ldg;
     const int* cperm;
     const int* cptr;
     float* partial;  // [R][N][Bpad]
@@ -88,33 +89,21 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_grad_x_narrow_kernel(GxNarrow
         // covers 8 consecutive rows x BPL slots of one granule -> 32 distinct banks.
         // Item u = (granule gl, row ol): BPL coalesced 4-byte loads (lanes run along o), one
         // vector store of the granule.  Four items are in flight per thread.
+        // The tile comes from the transposed gradient gT[L][ldg]: row ol is BT contiguous floats,
+        // copied granule by granule (one 4/8/16-byte cp.async per lane, a warp covers one row).
         {
             const int totalItems = T * 32;
-            constexpr int kBatch = 4;
-            for (int u0 = tid; u0 < totalItems; u0 += kThreads * kBatch) {
-                float v[kBatch][BPL];
-#pragma unroll
-                for (int k = 0; k < kBatch; ++k) {
-                    const int u = u0 + k * kThreads;
-                    const int gl = u / T, ol = u - gl * T;
-#pragma unroll
-                    for (int q = 0; q < BPL; ++q) {
-                        const int b = b0 + gl * GR + q;
-                        v[k][q] = (u < totalItems && ol < nrows && b < p.B)
-                                      ? __ldg(p.g + static_cast<size_t>(b) * L + o0 + ol)
-                                      : 0.f;
-                    }
-                }
-#pragma unroll
-                for (int k = 0; k < kBatch; ++k) {
-                    const int u = u0 + k * kThreads;
-                    const int gl = u / T, ol = u - gl * T;
-                    if (u < totalItems) {
-                        float* dst = g_s + static_cast<size_t>(ol) * BT + ((gl ^ (ol & SW)) * GR);
-                        store_vec<BPL>(dst, v[k]);
-                    }
+            for (int u = tid; u < totalItems; u += kThreads) {
+                const int ol = u >> 5, gl = u & 31;
+                float* dst = g_s + static_cast<size_t>(ol) * BT + ((gl ^ (ol & SW)) * GR);
+                if (ol < nrows) {
+                    __pipeline_memcpy_async(dst, p.gT + static_cast<size_t>(o0 + ol) * p.ldg + b0 + gl * GR, 4 * GR);
+                } else {
+                    const float zero[BPL] = {};
+                    store_vec<BPL>(dst, zero);
                 }
             }
+            __pipeline_commit();
         }
 
         // (2) run offsets of my input slice and the staged entries.
@@ -214,22 +203,28 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, float*
 
 // ---- wide inputs -------------------------------------------------------------------
 
-// One warp per (input i, batch tile of 128): walks row i of the canonical index.
+// One warp per (input i, batch tile of 32*VEC): walks row i of the canonical index and gathers
+// one row of the transposed gradient gT[L][ldg] per entry.
+template <int VEC>
 __global__ void __launch_bounds__(256) ffi_grad_x_wide_kernel(const float* __restrict__ W,
                                                               const float* __restrict__ gT,
                                                               const int* __restrict__ rowptr,
                                                               const int* __restrict__ perm,
                                                               float* __restrict__ gx, int B, int N,
-                                                              int K, int Bpad, int x_transposed) {
+                                                              int K, long long ldg, int x_transposed) {
+    using V = typename Vec<VEC>::type;
+    constexpr int BTW = 32 * VEC;
     const int lane = threadIdx.x & 31;
     const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int nBT = Bpad / 128;
+    const int nBT = static_cast<int>(ldg / BTW);
     if (wid >= static_cast<long long>(N) * nBT) return;
     const int i = static_cast<int>(wid / nBT);
     const int bt = static_cast<int>(wid - static_cast<long long>(i) * nBT);
-    const float4* gT4 = reinterpret_cast<const float4*>(gT + bt * 128) + lane;
-    const size_t ld4 = Bpad / 4;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const V* gTv = reinterpret_cast<const V*>(gT + bt * BTW) + lane;
+    const size_t ldv = static_cast<size_t>(ldg / VEC);
+    float acc[VEC];
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) acc[q] = 0.f;
     const int s = rowptr[i], t = rowptr[i + 1];
     for (int base = s; base < t; base += 32) {
         const int e = base + lane;
@@ -244,20 +239,17 @@ __global__ void __launch_bounds__(256) ffi_grad_x_wide_kernel(const float* __res
         for (int u = 0; u < cnt; ++u) {
             const int ou = __shfl_sync(0xffffffffu, o, u);
             const float wu = __shfl_sync(0xffffffffu, w, u);
-            const float4 v = __ldg(gT4 + static_cast<size_t>(ou) * ld4);
-            acc.x = fmaf(wu, v.x, acc.x);
-            acc.y = fmaf(wu, v.y, acc.y);
-            acc.z = fmaf(wu, v.z, acc.z);
-            acc.w = fmaf(wu, v.w, acc.w);
+            const V v = __ldg(gTv + static_cast<size_t>(ou) * ldv);
+#pragma unroll
+            for (int q = 0; q < VEC; ++q) acc[q] = fmaf(wu, vec_get(v, q), acc[q]);
         }
     }
-    const int b = bt * 128 + lane * 4;
-    const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+    const int b = bt * BTW + lane * VEC;
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < VEC; ++q) {
         if (b + q < B) {
-            if (x_transposed) gx[static_cast<size_t>(i) * B + b + q] = vals[q];
-            else gx[static_cast<size_t>(b + q) * N + i] = vals[q];
+            if (x_transposed) gx[static_cast<size_t>(i) * B + b + q] = acc[q];
+            else gx[static_cast<size_t>(b + q) * N + i] = acc[q];
         }
     }
 }
@@ -304,8 +296,8 @@ bool narrow_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, Narro
 }
 
 __global__ void transpose_g_kernel(const float* __restrict__ g, float* __restrict__ gT, int B,
-                                   long long L, int Bpad) {
-    // g [B][L] -> gT [L][Bpad] (zero padded batch)
+                                   long long L, long long ldg) {
+    // g [B][L] -> gT [L][ldg] (zero padded batch)
     __shared__ float tile[32][33];
     const long long o0 = static_cast<long long>(blockIdx.x) * 32;
     const int b0 = blockIdx.y * 32;
@@ -318,20 +310,38 @@ __global__ void transpose_g_kernel(const float* __restrict__ g, float* __restric
     for (int dy = threadIdx.y; dy < 32; dy += blockDim.y) {
         const long long o = o0 + dy;
         const int b = b0 + threadIdx.x;
-        if (o < L && b < Bpad) gT[static_cast<size_t>(o) * Bpad + b] = tile[threadIdx.x][dy];
+        if (o < L && b < ldg) gT[static_cast<size_t>(o) * ldg + b] = tile[threadIdx.x][dy];
     }
 }
 
 }  // namespace
 
+int64_t transposed_g_stride(int64_t B) { return B <= 32 ? 32 : (B <= 64 ? 64 : round_up(B, 128)); }
+
+int launch_transpose_g(const float* g, float* gT, int B, int64_t L, int64_t ldg, cudaStream_t stream) {
+    dim3 block(32, 8);
+    const long long blocks_o = ceil_div(L, 32);
+    if (blocks_o > 2147483647LL) return fail(FFI_ERR_UNSUPPORTED, "L too large");
+    dim3 grid(static_cast<unsigned>(blocks_o), static_cast<unsigned>(ldg / 32));
+    transpose_g_kernel<<<grid, block, 0, stream>>>(g, gT, B, L, ldg);
+    FFI_LAUNCH_CHECK("transpose_g_kernel");
+    return FFI_OK;
+}
+
+bool grad_x_narrow_applicable(const ffi_plan* plan, int64_t B) {
+    DeviceInfo dev;
+    if (!plan || get_device_info(&dev) != FFI_OK) return false;
+    NarrowConfig c;
+    return narrow_config(plan, B, dev, &c);
+}
+
+// Scratch beyond gT: the range partials of the narrow kernel (the wide kernel needs none).
 size_t grad_x_workspace_bytes(const ffi_plan* plan, int64_t B) {
     DeviceInfo dev;
     if (get_device_info(&dev) != FFI_OK) return 0;
     NarrowConfig c;
-    if (narrow_config(plan, B, dev, &c))
-        return static_cast<size_t>(c.R) * plan->N * c.Bpad * 4;
-    const size_t Bpad = static_cast<size_t>(round_up(B, 128));
-    return static_cast<size_t>(plan->L) * Bpad * 4;
+    if (narrow_config(plan, B, dev, &c)) return static_cast<size_t>(c.R) * plan->N * c.Bpad * 4;
+    return 0;
 }
 
 int launch_grad_x(const GradXArgs& a, cudaStream_t stream) {
@@ -339,17 +349,21 @@ int launch_grad_x(const GradXArgs& a, cudaStream_t stream) {
     int rc = get_device_info(&dev);
     if (rc != FFI_OK) return rc;
     const ffi_plan* plan = a.plan;
-    const size_t need = grad_x_workspace_bytes(plan, a.B);
-    if (!a.workspace || a.workspace_bytes < need)
-        return fail(FFI_ERR_WORKSPACE, "grad_x needs %zu bytes of workspace, got %zu", need, a.workspace_bytes);
-    if (reinterpret_cast<uintptr_t>(a.workspace) % 16 != 0)
-        return fail(FFI_ERR_WORKSPACE, "workspace must be 16-byte aligned");
+    if (!a.gT || a.ldg < a.B || a.ldg % 32 != 0)
+        return fail(FFI_ERR_INVALID_ARGUMENT, "grad_x needs the transposed upstream gradient");
 
     NarrowConfig c;
     if (narrow_config(plan, a.B, dev, &c)) {
+        const size_t need = grad_x_workspace_bytes(plan, a.B);
+        if (!a.workspace || a.workspace_bytes < need)
+            return fail(FFI_ERR_WORKSPACE, "grad_x needs %zu bytes of workspace, got %zu", need, a.workspace_bytes);
+        if (reinterpret_cast<uintptr_t>(a.workspace) % 16 != 0)
+            return fail(FFI_ERR_WORKSPACE, "workspace must be 16-byte aligned");
+        if (a.ldg < c.Bpad) return fail(FFI_ERR_INVALID_ARGUMENT, "transposed gradient stride too small");
         GxNarrowParams p;
         p.W = a.W;
-        p.g = a.g;
+        p.gT = a.gT;
+        p.ldg = a.ldg;
         p.cperm = plan->cperm;
         p.cptr = plan->cptr;
         p.partial = static_cast<float*>(a.workspace);
@@ -373,20 +387,19 @@ int launch_grad_x(const GradXArgs& a, cudaStream_t stream) {
         return FFI_OK;
     }
 
-    // Wide inputs.
-    const int Bpad = static_cast<int>(round_up(a.B, 128));
-    float* gT = static_cast<float*>(a.workspace);
-    {
-        dim3 block(32, 8);
-        const long long gx_blocks = ceil_div(a.L, 32);
-        if (gx_blocks > 2147483647LL) return fail(FFI_ERR_UNSUPPORTED, "L too large");
-        dim3 grid(static_cast<unsigned>(gx_blocks), static_cast<unsigned>(Bpad / 32));
-        transpose_g_kernel<<<grid, block, 0, stream>>>(a.g, gT, a.B, a.L, Bpad);
-        FFI_LAUNCH_CHECK("transpose_g_kernel");
-    }
-    const long long warps = static_cast<long long>(a.N) * (Bpad / 128);
-    ffi_grad_x_wide_kernel<<<static_cast<unsigned>(ceil_div(warps, 8)), 256, 0, stream>>>(
-        a.W, gT, plan->rowptr, plan->perm, a.gx, a.B, a.N, a.K, Bpad, a.x_transposed);
+    // Wide inputs: one warp per (input, batch tile) over the canonical index.
+    const int vec = a.ldg % 128 == 0 ? 4 : (a.ldg % 64 == 0 ? 2 : 1);
+    const long long warps = static_cast<long long>(a.N) * (a.ldg / (32 * vec));
+    const unsigned blocks = static_cast<unsigned>(ceil_div(warps, 8));
+    if (vec == 4)
+        ffi_grad_x_wide_kernel<4><<<blocks, 256, 0, stream>>>(a.W, a.gT, plan->rowptr, plan->perm, a.gx, a.B, a.N,
+                                                              a.K, a.ldg, a.x_transposed);
+    else if (vec == 2)
+        ffi_grad_x_wide_kernel<2><<<blocks, 256, 0, stream>>>(a.W, a.gT, plan->rowptr, plan->perm, a.gx, a.B, a.N,
+                                                              a.K, a.ldg, a.x_transposed);
+    else
+        ffi_grad_x_wide_kernel<1><<<blocks, 256, 0, stream>>>(a.W, a.gT, plan->rowptr, plan->perm, a.gx, a.B, a.N,
+                                                              a.K, a.ldg, a.x_transposed);
     FFI_LAUNCH_CHECK("ffi_grad_x_wide_kernel");
     return FFI_OK;
 }
