@@ -30,6 +30,7 @@ EXPORTED_SYMBOLS = (
     "ffi_forward_workspace_bytes", "ffi_forward",
     "ffi_plan_create", "ffi_plan_destroy", "ffi_plan_info", "ffi_plan_export", "ffi_plan_export_chunked",
     "ffi_backward_workspace_bytes", "ffi_backward",
+    "ffi_grad_x_static_max_scratch_bytes", "ffi_grad_x_static",
     "ffi_bce_workspace_bytes", "ffi_bce_grad", "ffi_adam_step",
 )
 
@@ -69,6 +70,10 @@ def _declare(lib):
     lib.ffi_backward_workspace_bytes.argtypes = [vp, i64, i64, i64, i64, i32, i32, i32, i32]
     lib.ffi_backward.restype = i32
     lib.ffi_backward.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp, sz, vp]
+    lib.ffi_grad_x_static_max_scratch_bytes.restype = sz
+    lib.ffi_grad_x_static_max_scratch_bytes.argtypes = []
+    lib.ffi_grad_x_static.restype = i32
+    lib.ffi_grad_x_static.argtypes = [vp, vp, i64, vp, vp, i64, i64, i64, i64, i32, vp]
     lib.ffi_bce_workspace_bytes.restype = sz
     lib.ffi_bce_workspace_bytes.argtypes = [i64, i64]
     lib.ffi_bce_grad.restype = i32

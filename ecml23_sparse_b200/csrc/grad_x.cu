@@ -21,6 +21,8 @@
 // Wide inputs: g is transposed once into gT[L][Bpad] (workspace) and one warp per
 // (input, batch tile) walks the canonical row, gathering 128 contiguous batch values
 // per entry.
+#include <mutex>
+
 #include "ffi_common.cuh"
 
 namespace ffi {
@@ -405,3 +407,82 @@ int launch_grad_x(const GradXArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace ffi
+
+// ---- allocation-free entry point ------------------------------------------------------
+//
+// Some hosts of this library may not allocate device memory at the point where they call
+// it: a TensorFlow or PyTorch op kernel is expected to take scratch from the framework's own
+// allocator (which has usually reserved almost all of the GPU, so a raw cudaMalloc can fail
+// or force a device-wide synchronisation), and a serving loop that has already started
+// steady-state execution cannot afford cudaMalloc's implicit synchronisation either.  For
+// those callers ffi_grad_x_static runs the narrow-input grad_x kernel with its range partials
+// in a fixed array that lives in the library image instead of in a caller workspace.
+namespace ffi {
+namespace {
+
+constexpr size_t kStaticScratchBytes = static_cast<size_t>(20) << 20;  // 20 MiB per GPU that loads the library
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle of the symbol, not a device address: the
+// address each device gave the array is looked up once per device, with that device current.
+int static_scratch_address(void** out) {
+    static std::mutex mu;
+    static void* addr[64] = {};
+    int dev = 0;
+    FFI_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(FFI_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!addr[dev]) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr)
+            return fail(FFI_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
+        addr[dev] = ptr;
+    }
+    *out = addr[dev];
+    return FFI_OK;
+}
+
+}  // namespace
+}  // namespace ffi
+
+extern "C" size_t ffi_grad_x_static_max_scratch_bytes(void) { return ffi::kStaticScratchBytes; }
+
+extern "C" int ffi_grad_x_static(const float* W, const float* gT, int64_t ldg, const ffi_plan* plan, float* grad_x,
+                                 int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed, void* stream_v) {
+    using namespace ffi;
+    if (!W || !gT || !plan || !grad_x) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL argument to ffi_grad_x_static");
+    if (B <= 0 || N <= 0 || L <= 0 || K <= 0 || B >= (1LL << 31))
+        return fail(FFI_ERR_INVALID_ARGUMENT, "B, N, L, K must be positive");
+    if (plan->L != L || plan->K != K || plan->N != N)
+        return fail(FFI_ERR_STALE_PLAN, "plan was built for (L,K,N)=(%lld,%lld,%lld), call has (%lld,%lld,%lld)",
+                    (long long)plan->L, (long long)plan->K, (long long)plan->N, (long long)L, (long long)K,
+                    (long long)N);
+    if (ldg < B || ldg % 32 != 0 || reinterpret_cast<uintptr_t>(gT) % 16 != 0)
+        return fail(FFI_ERR_INVALID_ARGUMENT, "gT must be 16-byte aligned with a row stride that is a multiple of 32 and >= B");
+    const size_t need = grad_x_workspace_bytes(plan, B);
+    if (need > kStaticScratchBytes)
+        return fail(FFI_ERR_WORKSPACE,
+                    "ffi_grad_x_static: this shape needs %zu bytes of scratch, the built-in array holds %zu; "
+                    "use ffi_backward with a caller workspace",
+                    need, kStaticScratchBytes);
+    void* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc != FFI_OK) return rc;
+    GradXArgs a;
+    a.idx = nullptr;
+    a.W = W;
+    a.g = nullptr;
+    a.gT = gT;
+    a.ldg = ldg;
+    a.plan = plan;
+    a.gx = grad_x;
+    a.x_transposed = x_transposed;
+    a.B = static_cast<int>(B);
+    a.N = static_cast<int>(N);
+    a.L = static_cast<int>(L);
+    a.K = static_cast<int>(K);
+    a.workspace = scratch;
+    a.workspace_bytes = kStaticScratchBytes;
+    return launch_grad_x(a, static_cast<cudaStream_t>(stream_v));
+}

@@ -121,6 +121,40 @@ int ffi_backward(const void* x, const int32_t* idx, const void* W, const float* 
                  int64_t N, int64_t L, int64_t K, int x_transposed, int dtype, void* workspace,
                  size_t workspace_bytes, void* stream);
 
+/*
+ * grad_x without any allocation and without a caller workspace.  This entry point has no
+ * counterpart in the reference.
+ *
+ * Who it is for: callers that must not allocate device memory at the call site.  An op kernel
+ * inside TensorFlow or PyTorch is supposed to get its scratch from the framework's allocator,
+ * which normally owns nearly all GPU memory already, so a raw cudaMalloc there may fail or
+ * stall every stream; a latency-bound serving loop cannot accept cudaMalloc's device-wide
+ * synchronisation either.  Here the scratch of the narrow-input grad_x kernel (its per-range
+ * partial sums) lives in a fixed __device__ array inside the library: 20 MiB
+ * (ffi_grad_x_static_max_scratch_bytes()), held by every GPU that loads the library until the
+ * process exits.  The call performs no cudaMalloc/cudaFree and calls no allocating routine.
+ *
+ * Inputs: W[L,K]; gT, the upstream gradient ALREADY transposed to [L][ldg] (batch contiguous,
+ * ldg a multiple of 32 and >= B, columns B..ldg-1 zero, 16-byte aligned) - the transposed copy
+ * that ffi_backward builds inside its workspace is an input here; the plan of idx.
+ * Output: grad_x in the layout of x ([N,B] when x_transposed, else [B,N]).
+ *
+ * Limits and rules:
+ *  - shapes whose partial sums exceed the array (roughly (SMs/ceil(N/256)) * N * roundup(B) * 4
+ *    bytes; the headline shape B=128, N=768 needs 18.4 MiB) are refused with FFI_ERR_WORKSPACE;
+ *    use ffi_backward with a caller workspace for those;
+ *  - the first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress): make that first call before starting any stream capture;
+ *  - all calls on a device share the one array, so two calls that may overlap on the GPU
+ *    (different streams) race with each other: serialise them.  The array keeps the previous
+ *    call's contents; nothing has to be cleared because every word a call reads it has
+ *    written before in the same call.
+ */
+size_t ffi_grad_x_static_max_scratch_bytes(void);
+int ffi_grad_x_static(const float* W, const float* gT, int64_t ldg, const ffi_plan* plan,
+                      float* grad_x, int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed,
+                      void* stream);
+
 /* ------------------------------------------------------------ loss / Adam ---- */
 
 /*

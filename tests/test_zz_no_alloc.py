@@ -1,0 +1,79 @@
+"""GPU test of ffi_grad_x_static, the grad_x entry point for callers that may not allocate.
+
+Framework op kernels and steady-state serving loops cannot call cudaMalloc where they call this
+library; ffi_grad_x_static therefore keeps its scratch in a fixed array inside the library.  The
+test drives it through the C ABI exactly as such a caller would (raw pointers, no workspace) and
+compares with grad_x of the regular entry point ffi_backward, twice in a row with different data
+so that the second call runs on top of the first call's leftovers in the shared array.
+
+Collected last (file name), so a run that stops at the first failure has run everything else.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import ecml23_sparse_b200 as ffi
+from ecml23_sparse_b200 import _lib, synth
+from ecml23_sparse_b200.ops import _backward, _stream_ptr
+
+pytestmark = pytest.mark.gpu
+
+
+def _transposed_gradient(g: torch.Tensor) -> torch.Tensor:
+    """[B,L] -> [L][ldg] with the batch zero padded to a multiple of 32 (what the entry point takes)."""
+    B, L = g.shape
+    ldg = 32 if B <= 32 else (64 if B <= 64 else -(-B // 128) * 128)
+    gT = torch.zeros((L, ldg), dtype=torch.float32, device=g.device)
+    gT[:, :B] = g.t()
+    return gT
+
+
+def _static_grad_x(W, gT, plan, B, N, L, K, transposed):
+    out = torch.empty((N, B) if transposed else (B, N), dtype=torch.float32, device=W.device)
+    lib = _lib.load()
+    with torch.cuda.device(W.device):
+        _lib.check(lib.ffi_grad_x_static(W.data_ptr(), gT.data_ptr(), gT.shape[1], plan.handle, out.data_ptr(),
+                                         B, N, L, K, int(transposed), _stream_ptr(W.device)))
+    return out
+
+
+@pytest.mark.parametrize("shape,transposed", [((128, 768, 20_011, 32), True), ((37, 254, 513, 16), False)])
+def test_static_scratch_grad_x_matches_regular_entry_point_twice(cuda_device, shape, transposed):
+    dev = cuda_device
+    B, N, L, K = shape
+    idx = synth.indices_without_replacement(31, 0, L, K, N, device=dev)
+    plan = ffi.FFIPlan(idx, N)
+    x = synth.normal(31, 1, (N, B) if transposed else (B, N), device=dev)
+    for call in range(2):
+        W = synth.normal(31, 10 + call, (L, K), std=0.2, device=dev)
+        g = synth.normal(31, 20 + call, (B, L), device=dev)
+        expected, _, _ = _backward(x, idx, W, g, transposed, plan=plan, want_weight_grad=False)
+        got = _static_grad_x(W, _transposed_gradient(g), plan, B, N, L, K, transposed)
+        torch.cuda.synchronize()
+        # same kernel, same launch geometry, same summation order: the results agree to the last bit,
+        # which is well inside the 1e-5 tolerance the other grad_x tests use
+        assert torch.allclose(got, expected, rtol=1e-5, atol=1e-5)
+        assert torch.equal(got, expected)
+
+
+def test_static_scratch_rejects_oversize_and_bad_arguments(cuda_device):
+    dev = cuda_device
+    lib = _lib.load()
+    limit = lib.ffi_grad_x_static_max_scratch_bytes()
+    assert limit == 20 << 20
+    B, N, L, K = 4096, 2048, 512, 8  # one range of partial sums alone is 2048*4096*4 = 32 MiB
+    idx = synth.indices_without_replacement(5, 0, L, K, N, device=dev)
+    plan = ffi.FFIPlan(idx, N)
+    W = torch.zeros((L, K), device=dev)
+    gT = torch.zeros((L, 4096), device=dev)
+    out = torch.empty((B, N), device=dev)
+    rc = lib.ffi_grad_x_static(W.data_ptr(), gT.data_ptr(), 4096, plan.handle, out.data_ptr(), B, N, L, K, 0,
+                               _stream_ptr(dev))
+    assert rc == 3 and b"scratch" in lib.ffi_last_error()
+    assert lib.ffi_grad_x_static(None, gT.data_ptr(), 4096, plan.handle, out.data_ptr(), B, N, L, K, 0, None) == 1
+    assert lib.ffi_grad_x_static(W.data_ptr(), gT.data_ptr(), 4000, plan.handle, out.data_ptr(), B, N, L, K, 0,
+                                 None) == 1
+    assert lib.ffi_grad_x_static(W.data_ptr(), gT.data_ptr(), 4096, plan.handle, out.data_ptr(), B, N, L + 1, K, 0,
+                                 None) == 5
