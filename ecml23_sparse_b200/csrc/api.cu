@@ -162,7 +162,11 @@ extern "C" size_t ffi_backward_workspace_bytes(const ffi_plan* plan, int64_t B, 
         const bool smem = grad_w_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
         total += plan_x(smem, B, N, x_transposed).bytes;
     }
-    if (want_grad_x && plan) total += align_up(grad_x_workspace_bytes(plan, B));
+    if (want_grad_x && plan) {
+        const size_t sep = grad_x_workspace_bytes(plan, B), fus = backward_fused_workspace_bytes(plan, B);
+        total += align_up(sep > fus ? sep : fus);
+        total += align_up(static_cast<size_t>(N) * round_up(B, 128) * 4);  // xT copy of the fused kernel
+    }
     // the transposed upstream gradient gT[L][ldg], shared by grad_x and the barrier-free grad_W kernel
     if (want_grad_x || (want_grad_w && K % 4 == 0))
         total += align_up(static_cast<size_t>(L) * transposed_g_stride(B) * 4);
@@ -189,33 +193,81 @@ extern "C" int ffi_backward(const void* x, const int32_t* idx, const void* W, co
     size_t used = 0;
     if (workspace && reinterpret_cast<uintptr_t>(workspace) % kAlign != 0)
         return fail(FFI_ERR_WORKSPACE, "workspace must be %zu-byte aligned", kAlign);
+    auto take = [&](size_t bytes, const char* what, void** out) -> int {
+        bytes = align_up(bytes);
+        if (!workspace || workspace_bytes < used + bytes)
+            return fail(FFI_ERR_WORKSPACE, "ffi_backward needs %zu more bytes of workspace for %s", bytes, what);
+        *out = ws + used;
+        used += bytes;
+        return FFI_OK;
+    };
+    const int Bi = static_cast<int>(B), Ni = static_cast<int>(N), Li = static_cast<int>(L), Ki = static_cast<int>(K);
 
-    // g transposed to [L][ldg] once, for the kernels that read whole batch rows of g.
-    const bool gw_stream = (grad_w || grad_bias) &&
-                           grad_w_stream_applicable(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), idx);
+    // One pass for grad_x and grad_W when the shape allows it, else one kernel each.
+    const bool fused = grad_x && grad_w && backward_fused_applicable(plan, B);
+    const bool sep_w = !fused && (grad_w || grad_bias);
+    const bool gw_stream = sep_w && grad_w_stream_applicable(Bi, Ni, Ki, idx);
+
+    // g transposed to [L][ldg] once, for the kernels that read whole batch rows of g; the same
+    // pass produces grad_bias.
     const float* gT = nullptr;
     const int64_t ldg = transposed_g_stride(B);
+    bool bias_done = false;
     if (grad_x || gw_stream) {
-        const size_t bytes = align_up(static_cast<size_t>(L) * ldg * 4);
-        if (!workspace || workspace_bytes < used + bytes)
-            return fail(FFI_ERR_WORKSPACE, "ffi_backward needs %zu bytes of workspace for the transposed gradient", bytes);
-        float* dst = reinterpret_cast<float*>(ws + used);
-        rc = launch_transpose_g(g, dst, static_cast<int>(B), L, ldg, stream);
+        void* dst = nullptr;
+        rc = take(static_cast<size_t>(L) * ldg * 4, "the transposed gradient", &dst);
         if (rc != FFI_OK) return rc;
-        gT = dst;
-        used += bytes;
+        rc = launch_transpose_g(g, static_cast<float*>(dst), grad_bias, Bi, L, ldg, stream);
+        if (rc != FFI_OK) return rc;
+        gT = static_cast<const float*>(dst);
+        bias_done = grad_bias != nullptr;
     }
 
-    if (grad_w || grad_bias) {
-        const bool smem = grad_w_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
-        const XPlan xp = plan_x(smem, B, N, x_transposed);
-        if (xp.copy && (!workspace || workspace_bytes < used + xp.bytes))
-            return fail(FFI_ERR_WORKSPACE, "ffi_backward needs %zu more bytes of workspace for x", xp.bytes);
-        const float* xT = nullptr;
-        rc = stage_x(xp, static_cast<const float*>(x), reinterpret_cast<float*>(ws + used), B, N, x_transposed,
-                     stream, &xT);
+    GradXArgs ax;
+    ax.idx = idx;
+    ax.W = static_cast<const float*>(W);
+    ax.g = g;
+    ax.gT = gT;
+    ax.ldg = ldg;
+    ax.plan = plan;
+    ax.gx = grad_x;
+    ax.x_transposed = x_transposed;
+    ax.B = Bi;
+    ax.N = Ni;
+    ax.L = Li;
+    ax.K = Ki;
+
+    if (fused) {
+        const float* xT = static_cast<const float*>(x);
+        int64_t ldx = B;
+        if (!x_transposed) {
+            ldx = round_up(B, 128);
+            void* dst = nullptr;
+            rc = take(static_cast<size_t>(N) * ldx * 4, "the transposed x", &dst);
+            if (rc != FFI_OK) return rc;
+            rc = launch_transpose_pad(static_cast<const float*>(x), static_cast<float*>(dst), Bi, Ni, ldx, stream);
+            if (rc != FFI_OK) return rc;
+            xT = static_cast<const float*>(dst);
+        }
+        void* part = nullptr;
+        rc = take(backward_fused_workspace_bytes(plan, B), "the grad_x partial sums", &part);
         if (rc != FFI_OK) return rc;
-        used += xp.bytes;
+        ax.workspace = part;
+        ax.workspace_bytes = workspace_bytes - (static_cast<unsigned char*>(part) - ws);
+        return launch_backward_fused(ax, xT, ldx, grad_w, stream);
+    }
+
+    if (grad_w || (grad_bias && !bias_done)) {
+        const bool smem = grad_w_uses_smem_x(Bi, Ni, Ki, nullptr);
+        const XPlan xp = plan_x(smem, B, N, x_transposed);
+        void* xdst = nullptr;
+        if (xp.copy) {
+            rc = take(xp.bytes, "x", &xdst);
+            if (rc != FFI_OK) return rc;
+        }
+        const float* xT = nullptr;
+        rc = stage_x(xp, static_cast<const float*>(x), static_cast<float*>(xdst), B, N, x_transposed, stream, &xT);
+        if (rc != FFI_OK) return rc;
         GradWArgs a;
         a.xT = xT;
         a.ldx = xp.ld;
@@ -224,31 +276,18 @@ extern "C" int ffi_backward(const void* x, const int32_t* idx, const void* W, co
         a.gT = gT;
         a.ldg = ldg;
         a.gW = grad_w;
-        a.gbias = grad_bias;
-        a.B = static_cast<int>(B);
-        a.N = static_cast<int>(N);
-        a.L = static_cast<int>(L);
-        a.K = static_cast<int>(K);
+        a.gbias = bias_done ? nullptr : grad_bias;
+        a.B = Bi;
+        a.N = Ni;
+        a.L = Li;
+        a.K = Ki;
         rc = launch_grad_w(a, stream);
         if (rc != FFI_OK) return rc;
     }
     if (grad_x) {
-        GradXArgs a;
-        a.idx = idx;
-        a.W = static_cast<const float*>(W);
-        a.g = g;
-        a.gT = gT;
-        a.ldg = ldg;
-        a.plan = plan;
-        a.gx = grad_x;
-        a.x_transposed = x_transposed;
-        a.B = static_cast<int>(B);
-        a.N = static_cast<int>(N);
-        a.L = static_cast<int>(L);
-        a.K = static_cast<int>(K);
-        a.workspace = workspace ? ws + used : nullptr;
-        a.workspace_bytes = workspace_bytes > used ? workspace_bytes - used : 0;
-        rc = launch_grad_x(a, stream);
+        ax.workspace = workspace ? ws + used : nullptr;
+        ax.workspace_bytes = workspace_bytes > used ? workspace_bytes - used : 0;
+        rc = launch_grad_x(ax, stream);
         if (rc != FFI_OK) return rc;
     }
     return FFI_OK;

@@ -95,8 +95,10 @@ bool grad_w_stream_applicable(int B, int N, int K, const void* idx);
 
 // Row stride of the transposed upstream gradient gT[L][ldg] for a batch of B.
 int64_t transposed_g_stride(int64_t B);
-// g [B][L] -> gT [L][ldg], zero padded in the batch dimension.
-int launch_transpose_g(const float* g, float* gT, int B, int64_t L, int64_t ldg, cudaStream_t stream);
+// g [B][L] -> gT [L][ldg], zero padded in the batch dimension; gbias (nullable) receives the
+// column sums grad_bias[o] = sum_b g[b,o].
+int launch_transpose_g(const float* g, float* gT, float* gbias, int B, int64_t L, int64_t ldg,
+                       cudaStream_t stream);
 
 // x [B,N] -> xT [N][ldx] (zero padded to ldx), fp32.
 int launch_transpose_pad(const float* src, float* dst, int rows, int cols, int64_t ld_dst,
@@ -111,6 +113,8 @@ struct ffi_plan {
     int chunk_rows = 0;     // T: outputs per chunk of the chunked lists
     int64_t n_chunks = 0;   // ceil(L / T)
     bool has_chunks = false;
+    // largest number of entries any (chunk, slice of w consecutive inputs) holds, for w = 128, 256, 512, 1024
+    int max_slice_entries[4] = {0, 0, 0, 0};
     int32_t* rowptr = nullptr;  // [N+1]   canonical CSR-by-input
     int32_t* perm = nullptr;    // [L*K]   positions sorted by (idx[p], p)
     int32_t* cperm = nullptr;   // [L*K]   chunk-major: chunk c holds its T*K positions sorted by (idx[p], p)
@@ -137,5 +141,10 @@ size_t grad_x_workspace_bytes(const ffi_plan* plan, int64_t B);
 // True when launch_grad_x will take the register-accumulator kernel, which reads gT.
 bool grad_x_narrow_applicable(const ffi_plan* plan, int64_t B);
 int launch_grad_x(const GradXArgs& a, cudaStream_t stream);
+
+// grad_x and grad_W in one pass over the transposed index (narrow inputs, batch <= 128).
+bool backward_fused_applicable(const ffi_plan* plan, int64_t B);
+size_t backward_fused_workspace_bytes(const ffi_plan* plan, int64_t B);
+int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, float* gW, cudaStream_t stream);
 
 }  // namespace ffi

@@ -297,22 +297,46 @@ bool narrow_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, Narro
     return true;
 }
 
-__global__ void transpose_g_kernel(const float* __restrict__ g, float* __restrict__ gT, int B,
-                                   long long L, long long ldg) {
-    // g [B][L] -> gT [L][ldg] (zero padded batch)
-    __shared__ float tile[32][33];
+// g [B][L] -> gT [L][ldg] (zero padded batch), optionally with grad_bias[o] = sum_b g[b,o].
+// One block owns 32 outputs and walks the whole batch in slabs of 128, so the column sums are
+// complete inside the block and are added in a fixed order.
+__global__ void __launch_bounds__(256) transpose_g_kernel(const float* __restrict__ g, float* __restrict__ gT,
+                                                          float* __restrict__ gbias, int B, long long L,
+                                                          long long ldg) {
+    __shared__ float tile[128][33];
+    const int tid = threadIdx.x;
+    const int tx = tid & 31, ty = tid >> 5;   // load: tx = output, ty = batch row within a group of 8
+    const int bx = tid & 127, oy0 = tid >> 7; // store: bx = batch column, oy0 = first output row
     const long long o0 = static_cast<long long>(blockIdx.x) * 32;
-    const int b0 = blockIdx.y * 32;
-    for (int dy = threadIdx.y; dy < 32; dy += blockDim.y) {
-        const int b = b0 + dy;
-        const long long o = o0 + threadIdx.x;
-        tile[dy][threadIdx.x] = (b < B && o < L) ? g[static_cast<size_t>(b) * L + o] : 0.f;
+    const bool ocol = o0 + tx < L;
+    float colsum = 0.f;
+    for (long long bb = 0; bb < ldg; bb += 128) {
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            const long long b = bb + ty + 8 * u;
+            const float v = (ocol && b < B) ? __ldg(g + static_cast<size_t>(b) * L + o0 + tx) : 0.f;
+            tile[ty + 8 * u][tx] = v;
+            colsum += v;
+        }
+        __syncthreads();
+        if (bb + bx < ldg) {
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const int oy = oy0 + 2 * u;
+                if (o0 + oy < L) gT[static_cast<size_t>(o0 + oy) * ldg + bb + bx] = tile[bx][oy];
+            }
+        }
+        __syncthreads();
     }
-    __syncthreads();
-    for (int dy = threadIdx.y; dy < 32; dy += blockDim.y) {
-        const long long o = o0 + dy;
-        const int b = b0 + threadIdx.x;
-        if (o < L && b < ldg) gT[static_cast<size_t>(o) * ldg + b] = tile[threadIdx.x][dy];
+    if (gbias) {
+        tile[ty][tx] = colsum;
+        __syncthreads();
+        if (ty == 0 && ocol) {
+            float s = 0.f;
+#pragma unroll
+            for (int y = 0; y < 8; ++y) s += tile[y][tx];
+            gbias[o0 + tx] = s;
+        }
     }
 }
 
@@ -320,12 +344,10 @@ __global__ void transpose_g_kernel(const float* __restrict__ g, float* __restric
 
 int64_t transposed_g_stride(int64_t B) { return B <= 32 ? 32 : (B <= 64 ? 64 : round_up(B, 128)); }
 
-int launch_transpose_g(const float* g, float* gT, int B, int64_t L, int64_t ldg, cudaStream_t stream) {
-    dim3 block(32, 8);
+int launch_transpose_g(const float* g, float* gT, float* gbias, int B, int64_t L, int64_t ldg, cudaStream_t stream) {
     const long long blocks_o = ceil_div(L, 32);
     if (blocks_o > 2147483647LL) return fail(FFI_ERR_UNSUPPORTED, "L too large");
-    dim3 grid(static_cast<unsigned>(blocks_o), static_cast<unsigned>(ldg / 32));
-    transpose_g_kernel<<<grid, block, 0, stream>>>(g, gT, B, L, ldg);
+    transpose_g_kernel<<<static_cast<unsigned>(blocks_o), 256, 0, stream>>>(g, gT, gbias, B, L, ldg);
     FFI_LAUNCH_CHECK("transpose_g_kernel");
     return FFI_OK;
 }
@@ -486,3 +508,15 @@ extern "C" int ffi_grad_x_static(const float* W, const float* gT, int64_t ldg, c
     a.workspace_bytes = kStaticScratchBytes;
     return launch_grad_x(a, static_cast<cudaStream_t>(stream_v));
 }
+
+namespace ffi {
+// Shared with the fused backward kernel: grad_x = sum over ranges of partial[r][i][b], range order.
+int reduce_range_partials(const float* partial, float* gx, int R, int N, int B, int Bpad, int x_transposed,
+                          cudaStream_t stream) {
+    const long long total = static_cast<long long>(N) * Bpad;
+    reduce_partials_kernel<<<static_cast<unsigned>(ceil_div(total, 256)), 256, 0, stream>>>(partial, gx, R, N, B, Bpad,
+                                                                                           x_transposed);
+    FFI_LAUNCH_CHECK("reduce_partials_kernel");
+    return FFI_OK;
+}
+}  // namespace ffi

@@ -171,6 +171,20 @@ __global__ void chunk_fill_kernel(const int* __restrict__ perm, const int* __res
     }
 }
 
+// stats[j] = max over chunks c and slices s of (entries of chunk c whose input lies in
+// [s*w, (s+1)*w)), w = 128 << j.  Integer max is order independent.
+__global__ void slice_stats_kernel(const int* __restrict__ cptr, int N, long long nChunks, int* __restrict__ stats) {
+    const long long c = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (c >= nChunks) return;
+    const int* row = cptr + c * (N + 1);
+    for (int j = 0; j < 4; ++j) {
+        const int w = 128 << j;
+        int best = 0;
+        for (int lo = 0; lo < N; lo += w) best = max(best, row[min(N, lo + w)] - row[lo]);
+        atomicMax(stats + j, best);
+    }
+}
+
 // Self-check export: rebuild the canonical form from (cptr, cperm).
 __global__ void chunked_row_totals_kernel(const int* __restrict__ cptr, int N, long long nChunks,
                                           int* __restrict__ totals) {
@@ -324,6 +338,18 @@ extern "C" int ffi_plan_create(const int32_t* idx, int64_t L, int64_t K, int64_t
         chunk_fill_kernel<<<static_cast<unsigned>(nChunks), 256, (N + 1) * sizeof(int), stream>>>(
             plan->perm, lb.as<int>(), static_cast<int>(N), chunkEntries, plan->cptr, plan->cperm);
         FFI_LAUNCH_CHECK("chunk kernels");
+        // slice statistics for the kernels that stage one slice of a chunk in shared memory
+        DeviceBuffer stats;
+        if (stats.alloc(4 * sizeof(int)) != cudaSuccess) {
+            cudaGetLastError();
+            return cleanup(fail(FFI_ERR_ALLOC, "cudaMalloc of plan statistics failed"));
+        }
+        FFI_CUDA_CHECK(cudaMemsetAsync(stats.ptr, 0, 4 * sizeof(int), stream));
+        slice_stats_kernel<<<static_cast<unsigned>(ceil_div(nChunks, 256)), 256, 0, stream>>>(
+            plan->cptr, static_cast<int>(N), nChunks, stats.as<int>());
+        FFI_LAUNCH_CHECK("slice_stats_kernel");
+        FFI_CUDA_CHECK(cudaMemcpyAsync(plan->max_slice_entries, stats.ptr, 4 * sizeof(int), cudaMemcpyDeviceToHost,
+                                       stream));
         FFI_CUDA_CHECK(cudaStreamSynchronize(stream));
         plan->chunk_rows = T;
         plan->n_chunks = nChunks;
