@@ -31,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "ffi_plan_create", "ffi_plan_destroy", "ffi_plan_info", "ffi_plan_export", "ffi_plan_export_chunked",
     "ffi_backward_workspace_bytes", "ffi_backward",
     "ffi_grad_x_static_max_scratch_bytes", "ffi_grad_x_static",
+    "ffi_transposed_gradient_stride", "ffi_transpose_gradient",
     "ffi_bce_workspace_bytes", "ffi_bce_grad", "ffi_adam_step",
 )
 
@@ -74,6 +75,10 @@ def _declare(lib):
     lib.ffi_grad_x_static_max_scratch_bytes.argtypes = []
     lib.ffi_grad_x_static.restype = i32
     lib.ffi_grad_x_static.argtypes = [vp, vp, i64, vp, vp, i64, i64, i64, i64, i32, vp]
+    lib.ffi_transposed_gradient_stride.restype = i64
+    lib.ffi_transposed_gradient_stride.argtypes = [i64]
+    lib.ffi_transpose_gradient.restype = i32
+    lib.ffi_transpose_gradient.argtypes = [vp, vp, vp, i64, i64, vp]
     lib.ffi_bce_workspace_bytes.restype = sz
     lib.ffi_bce_workspace_bytes.argtypes = [i64, i64]
     lib.ffi_bce_grad.restype = i32

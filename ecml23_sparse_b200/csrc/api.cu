@@ -154,6 +154,18 @@ extern "C" int ffi_forward(const void* x, const int32_t* idx, const void* W, con
     return launch_forward(a, stream);
 }
 
+extern "C" int64_t ffi_transposed_gradient_stride(int64_t B) { return B > 0 ? transposed_g_stride(B) : 0; }
+
+extern "C" int ffi_transpose_gradient(const float* g, float* gT, float* grad_bias, int64_t B, int64_t L,
+                                      void* stream_v) {
+    if (!g || !gT) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_transpose_gradient");
+    if (B <= 0 || L <= 0 || B >= (1LL << 31) - 1 || L >= (1LL << 31) - 1)
+        return fail(FFI_ERR_INVALID_ARGUMENT, "B and L must be positive and fit 32 bits");
+    if (reinterpret_cast<uintptr_t>(gT) % 16 != 0) return fail(FFI_ERR_INVALID_ARGUMENT, "gT must be 16-byte aligned");
+    return launch_transpose_g(g, gT, grad_bias, static_cast<int>(B), L, transposed_g_stride(B),
+                              static_cast<cudaStream_t>(stream_v));
+}
+
 extern "C" size_t ffi_backward_workspace_bytes(const ffi_plan* plan, int64_t B, int64_t N, int64_t L, int64_t K,
                                                int x_transposed, int dtype, int want_grad_x, int want_grad_w) {
     if (check_shape(B, N, L, K) != FFI_OK || dtype != FFI_F32) return 0;

@@ -298,30 +298,32 @@ bool narrow_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, Narro
 }
 
 // g [B][L] -> gT [L][ldg] (zero padded batch), optionally with grad_bias[o] = sum_b g[b,o].
-// One block owns 32 outputs and walks the whole batch in slabs of 128, so the column sums are
-// complete inside the block and are added in a fixed order.
+// One block owns 64 outputs and walks the whole batch in slabs of 128, so the column sums are
+// complete inside the block and are added in a fixed order.  Rows of g start at arbitrary 4-byte
+// offsets (L is odd in practice), so a 256-byte row segment costs one extra 32-byte sector.
+constexpr int kTrO = 64;   // outputs per block
 __global__ void __launch_bounds__(256) transpose_g_kernel(const float* __restrict__ g, float* __restrict__ gT,
                                                           float* __restrict__ gbias, int B, long long L,
                                                           long long ldg) {
-    __shared__ float tile[128][33];
+    __shared__ float tile[128][kTrO + 1];
     const int tid = threadIdx.x;
-    const int tx = tid & 31, ty = tid >> 5;   // load: tx = output, ty = batch row within a group of 8
-    const int bx = tid & 127, oy0 = tid >> 7; // store: bx = batch column, oy0 = first output row
-    const long long o0 = static_cast<long long>(blockIdx.x) * 32;
+    const int tx = tid & (kTrO - 1), ty = tid / kTrO;  // load: tx = output, ty = batch row within a group of 4
+    const int bx = tid & 127, oy0 = tid >> 7;           // store: bx = batch column, oy0 = first output row
+    const long long o0 = static_cast<long long>(blockIdx.x) * kTrO;
     const bool ocol = o0 + tx < L;
     float colsum = 0.f;
     for (long long bb = 0; bb < ldg; bb += 128) {
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-            const long long b = bb + ty + 8 * u;
+        for (int u = 0; u < 32; ++u) {
+            const long long b = bb + ty + 4 * u;
             const float v = (ocol && b < B) ? __ldg(g + static_cast<size_t>(b) * L + o0 + tx) : 0.f;
-            tile[ty + 8 * u][tx] = v;
+            tile[ty + 4 * u][tx] = v;
             colsum += v;
         }
         __syncthreads();
         if (bb + bx < ldg) {
 #pragma unroll
-            for (int u = 0; u < 16; ++u) {
+            for (int u = 0; u < kTrO / 2; ++u) {
                 const int oy = oy0 + 2 * u;
                 if (o0 + oy < L) gT[static_cast<size_t>(o0 + oy) * ldg + bb + bx] = tile[bx][oy];
             }
@@ -334,7 +336,7 @@ __global__ void __launch_bounds__(256) transpose_g_kernel(const float* __restric
         if (ty == 0 && ocol) {
             float s = 0.f;
 #pragma unroll
-            for (int y = 0; y < 8; ++y) s += tile[y][tx];
+            for (int y = 0; y < 256 / kTrO; ++y) s += tile[y][tx];
             gbias[o0 + tx] = s;
         }
     }
@@ -345,7 +347,7 @@ __global__ void __launch_bounds__(256) transpose_g_kernel(const float* __restric
 int64_t transposed_g_stride(int64_t B) { return B <= 32 ? 32 : (B <= 64 ? 64 : round_up(B, 128)); }
 
 int launch_transpose_g(const float* g, float* gT, float* gbias, int B, int64_t L, int64_t ldg, cudaStream_t stream) {
-    const long long blocks_o = ceil_div(L, 32);
+    const long long blocks_o = ceil_div(L, kTrO);
     if (blocks_o > 2147483647LL) return fail(FFI_ERR_UNSUPPORTED, "L too large");
     transpose_g_kernel<<<static_cast<unsigned>(blocks_o), 256, 0, stream>>>(g, gT, gbias, B, L, ldg);
     FFI_LAUNCH_CHECK("transpose_g_kernel");

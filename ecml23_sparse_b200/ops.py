@@ -199,6 +199,21 @@ def _backward(features, lookup, weights, out_grad, transposed: bool, plan: Optio
     return gx, gw, gb
 
 
+def transpose_gradient(out_grad: torch.Tensor, want_bias_grad: bool = False):
+    """g[B,L] -> (gT[L][ldg] zero padded in the batch, grad_bias[L] or None): the transposed copy the
+    backward kernels read (and the input of the allocation-free grad_x entry point)."""
+    out_grad = _check_cuda("out_grad", out_grad, (torch.float32,))
+    B, L = out_grad.shape
+    lib = _lib.load()
+    ldg = int(lib.ffi_transposed_gradient_stride(B))
+    gT = torch.empty((L, ldg), dtype=torch.float32, device=out_grad.device)
+    gb = torch.empty((L,), dtype=torch.float32, device=out_grad.device) if want_bias_grad else None
+    with torch.cuda.device(out_grad.device):
+        _lib.check(lib.ffi_transpose_gradient(out_grad.data_ptr(), gT.data_ptr(), gb.data_ptr() if gb is not None else None,
+                                              B, L, _stream_ptr(out_grad.device)))
+    return gT, gb
+
+
 # ---- the reference's four wrappers (sparse/ops/fixed_fan_in_ops.py:15-28) -------------
 
 def fan_in_sparse_matmul(features, lookup, weights):

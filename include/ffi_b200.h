@@ -122,6 +122,18 @@ int ffi_backward(const void* x, const int32_t* idx, const void* W, const float* 
                  size_t workspace_bytes, void* stream);
 
 /*
+ * The upstream gradient transposed: g[B,L] -> gT[L][ldg] (batch contiguous, columns B..ldg-1
+ * zero), ldg = ffi_transposed_gradient_stride(B); grad_bias (nullable, [L]) receives
+ * sum_b g[b,o] from the same pass (TensorFlow's BiasAddGrad for sparse/layer.py:247).
+ * ffi_backward does this internally; the function is public because ffi_grad_x_static takes gT
+ * as an input, and because a loss kernel of the caller can produce gT directly and skip it.
+ * No counterpart in the reference (its kernels read g[B,L] column-wise, backward.cu.h:62-185).
+ */
+int64_t ffi_transposed_gradient_stride(int64_t B);
+int ffi_transpose_gradient(const float* g, float* gT, float* grad_bias, int64_t B, int64_t L,
+                           void* stream);
+
+/*
  * grad_x without any allocation and without a caller workspace.  This entry point has no
  * counterpart in the reference.
  *
