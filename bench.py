@@ -34,9 +34,9 @@ CPU_SAMPLE_DIVISOR = 16          # the CPU arms time L/16 of the outputs per ste
 SEED = 2023
 FMA_PER_CLK_PER_SM = 128
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
-# profiles/ (None until a capture of that kernel exists).
-NCU_TRAFFIC_BYTES = {"forward": None, "transpose_g": None, "backward_fused": None}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch at the headline shape, from the ncu capture
+# summarised in profiles/dram_traffic_headline_B128_N768_L670091_K32.md (None for other shapes).
+NCU_TRAFFIC_BYTES = {"forward": 194.3e6 + 302.0e6, "transpose_g": 343.1e6 + 299.2e6, "backward_fused": 523.6e6 + 114.0e6}
 
 
 def parse_args():
@@ -389,7 +389,7 @@ def run_ours(args):
     roofline = {
         "kernel": dk["kernel"], "bound": "hbm", "achieved": dk["achieved_gbs"], "peak": hbm_gbs, "unit": "GB/s",
         "frac": dk["achieved_gbs"] / hbm_gbs, "peak_kind": f"of {peak_kind}",
-        "traffic": NCU_TRAFFIC_BYTES.get(dominant),
+        "traffic": NCU_TRAFFIC_BYTES.get(dominant) if (B, N, Ls, K) == tuple(HEADLINE[k] for k in "BNLK") else None,
         "algorithmic_bytes_per_launch": dk["algorithmic_bytes"], "avg_launch_ms": dk["ms"],
         "step_roofline_ms": step_roof * 1e3, "step_frac_of_roofline": step_roof / (ms_per_step * 1e-3),
         "note": "limiter is the shared-memory gather pipe (128 B/clk/SM), not HBM: see profiles/",
