@@ -314,9 +314,10 @@ def run_ours(args):
             x_dev.copy_(x_host, non_blocking=True)
             rp_dev.copy_(rp_host, non_blocking=True)
             lab_dev.copy_(lab_host, non_blocking=True)
-            y = ops._forward(x_dev, idx, W, bias, False)
-            loss, gz = ffi.sparse_bce_with_logits(y, rp_dev, lab_dev, total_labels=L, label_offset=lo, inplace=True)
-            gx, gW, gb = ops._backward(x_dev, idx, W, gz, False, plan=plan, want_bias_grad=True)
+            # logits never reach HBM: the forward kernel's epilogue writes the BCE gradient, transposed
+            loss, gT = ops.forward_bce(x_dev, idx, W, bias, rp_dev, lab_dev, False, total_labels=L, label_offset=lo)
+            gx, gW, gb = ops._backward(x_dev, idx, W, gT, False, plan=plan, want_bias_grad=True,
+                                       grad_is_transposed=True)
             if world > 1:
                 dist.all_reduce(gx)
                 dist.all_reduce(loss)
@@ -329,8 +330,8 @@ def run_ours(args):
             "h2d_bytes_per_step": int(x_host.numel() * 4 + rp_host.numel() * 4 + lab_host.numel() * 4),
             "d2h_bytes_per_step": int(gx_host.numel() * 4 + 4),
             "ms_per_step": e2e_ms / args.steps,
-            "path": "pinned host x[B,N] + CSR targets -> FanInSparseMatmul(+bias) -> sigmoid-BCE grad -> "
-                    "FanInSparseMatmulGrad -> loss and grad_x to host",
+            "path": "pinned host x[B,N] + CSR targets -> FanInSparseMatmul(+bias) with fused sigmoid-BCE gradient -> "
+                    "FanInSparseMatmulGrad (grad_x, grad_W, grad_bias) -> loss and grad_x to host",
         }
 
     # ---- per-kernel times for the roofline (rank-local, each call timed alone) -------------

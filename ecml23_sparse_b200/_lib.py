@@ -32,6 +32,7 @@ EXPORTED_SYMBOLS = (
     "ffi_backward_workspace_bytes", "ffi_backward",
     "ffi_grad_x_static_max_scratch_bytes", "ffi_grad_x_static",
     "ffi_transposed_gradient_stride", "ffi_transpose_gradient",
+    "ffi_backward_from_transposed", "ffi_forward_bce_workspace_bytes", "ffi_forward_bce",
     "ffi_bce_workspace_bytes", "ffi_bce_grad", "ffi_adam_step",
 )
 
@@ -79,6 +80,12 @@ def _declare(lib):
     lib.ffi_transposed_gradient_stride.argtypes = [i64]
     lib.ffi_transpose_gradient.restype = i32
     lib.ffi_transpose_gradient.argtypes = [vp, vp, vp, i64, i64, vp]
+    lib.ffi_backward_from_transposed.restype = i32
+    lib.ffi_backward_from_transposed.argtypes = [vp, vp, vp, vp, i64, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp, sz, vp]
+    lib.ffi_forward_bce_workspace_bytes.restype = sz
+    lib.ffi_forward_bce_workspace_bytes.argtypes = [i64, i64, i64, i64, i32, i32]
+    lib.ffi_forward_bce.restype = i32
+    lib.ffi_forward_bce.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, vp, sz, vp]
     lib.ffi_bce_workspace_bytes.restype = sz
     lib.ffi_bce_workspace_bytes.argtypes = [i64, i64]
     lib.ffi_bce_grad.restype = i32

@@ -185,11 +185,12 @@ extern "C" size_t ffi_backward_workspace_bytes(const ffi_plan* plan, int64_t B, 
     return total;
 }
 
-extern "C" int ffi_backward(const void* x, const int32_t* idx, const void* W, const float* g,
-                            const ffi_plan* plan, float* grad_x, float* grad_w, float* grad_bias, int64_t B,
-                            int64_t N, int64_t L, int64_t K, int x_transposed, int dtype, void* workspace,
-                            size_t workspace_bytes, void* stream_v) {
-    if (!x || !idx || !W || !g) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_backward");
+// g is the upstream gradient [B,L]; alternatively gT_in (already transposed, stride ldg_in) is given.
+static int backward_impl(const void* x, const int32_t* idx, const void* W, const float* g, const float* gT_in,
+                         int64_t ldg_in, const ffi_plan* plan, float* grad_x, float* grad_w, float* grad_bias,
+                         int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed, int dtype, void* workspace,
+                         size_t workspace_bytes, void* stream_v) {
+    if (!x || !idx || !W || (!g && !gT_in)) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_backward");
     int rc = check_shape(B, N, L, K);
     if (rc != FFI_OK) return rc;
     if (dtype != FFI_F32) return fail(FFI_ERR_UNSUPPORTED, "ffi_backward: dtype %d not supported", dtype);
@@ -222,10 +223,20 @@ extern "C" int ffi_backward(const void* x, const int32_t* idx, const void* W, co
 
     // g transposed to [L][ldg] once, for the kernels that read whole batch rows of g; the same
     // pass produces grad_bias.
-    const float* gT = nullptr;
-    const int64_t ldg = transposed_g_stride(B);
+    const float* gT = gT_in;
+    const int64_t ldg = gT_in ? ldg_in : transposed_g_stride(B);
     bool bias_done = false;
-    if (grad_x || gw_stream) {
+    if (gT_in) {
+        if (ldg_in < B || ldg_in % 32 != 0 || reinterpret_cast<uintptr_t>(gT_in) % 16 != 0)
+            return fail(FFI_ERR_INVALID_ARGUMENT, "gT needs a row stride that is a multiple of 32 and >= B, 16-byte aligned");
+        if (sep_w && !gw_stream)
+            return fail(FFI_ERR_UNSUPPORTED, "this shape needs the untransposed gradient g[B,L] for grad_W");
+        if (grad_bias) {
+            rc = launch_bias_grad_rows(gT_in, ldg_in, L, grad_bias, stream);
+            if (rc != FFI_OK) return rc;
+            bias_done = true;
+        }
+    } else if (grad_x || gw_stream) {
         void* dst = nullptr;
         rc = take(static_cast<size_t>(L) * ldg * 4, "the transposed gradient", &dst);
         if (rc != FFI_OK) return rc;
@@ -303,4 +314,89 @@ extern "C" int ffi_backward(const void* x, const int32_t* idx, const void* W, co
         if (rc != FFI_OK) return rc;
     }
     return FFI_OK;
+}
+
+extern "C" int ffi_backward(const void* x, const int32_t* idx, const void* W, const float* g,
+                            const ffi_plan* plan, float* grad_x, float* grad_w, float* grad_bias, int64_t B,
+                            int64_t N, int64_t L, int64_t K, int x_transposed, int dtype, void* workspace,
+                            size_t workspace_bytes, void* stream_v) {
+    if (!g) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_backward");
+    return backward_impl(x, idx, W, g, nullptr, 0, plan, grad_x, grad_w, grad_bias, B, N, L, K, x_transposed, dtype,
+                         workspace, workspace_bytes, stream_v);
+}
+
+extern "C" int ffi_backward_from_transposed(const void* x, const int32_t* idx, const void* W, const float* gT,
+                                            int64_t ldg, const ffi_plan* plan, float* grad_x, float* grad_w,
+                                            float* grad_bias, int64_t B, int64_t N, int64_t L, int64_t K,
+                                            int x_transposed, int dtype, void* workspace, size_t workspace_bytes,
+                                            void* stream_v) {
+    if (!gT) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_backward_from_transposed");
+    return backward_impl(x, idx, W, nullptr, gT, ldg, plan, grad_x, grad_w, grad_bias, B, N, L, K, x_transposed, dtype,
+                         workspace, workspace_bytes, stream_v);
+}
+
+namespace ffi {
+int launch_forward_bce_stream(const FwdArgs& a, float* gT, int64_t ldg, float scale, double* loss_partials, int* ctas,
+                              cudaStream_t stream, bool* handled);
+int launch_bce_positive_fix(const float* xT, int64_t ldx, const int* idx, const float* W, const float* bias,
+                            const int* row_ptr, const int* labels, float* gT, int64_t ldg, float* loss,
+                            const double* partials, int nPartials, float scale, int B, int64_t L, int K,
+                            int64_t label_offset, cudaStream_t stream);
+constexpr size_t kBcePartialBytes = 1024 * sizeof(double);  // >= one partial per CTA of the forward kernel
+}  // namespace ffi
+
+extern "C" size_t ffi_forward_bce_workspace_bytes(int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed,
+                                                  int dtype) {
+    return ffi_forward_workspace_bytes(B, N, L, K, x_transposed, dtype) + kAlign + kBcePartialBytes;
+}
+
+extern "C" int ffi_forward_bce(const void* x, const int32_t* idx, const void* W, const float* bias,
+                               const int32_t* row_ptr, const int32_t* labels, float* gT, float* loss, int64_t B,
+                               int64_t N, int64_t L, int64_t K, int64_t L_total, int64_t label_offset, int x_transposed,
+                               int dtype, void* workspace, size_t workspace_bytes, void* stream_v) {
+    if (!x || !idx || !W || !row_ptr || !labels || !gT)
+        return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_forward_bce");
+    int rc = check_shape(B, N, L, K);
+    if (rc != FFI_OK) return rc;
+    if (dtype != FFI_F32) return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_bce: dtype %d not supported", dtype);
+    if (L_total < L) return fail(FFI_ERR_INVALID_ARGUMENT, "L_total must be >= L");
+    if (reinterpret_cast<uintptr_t>(gT) % 16 != 0) return fail(FFI_ERR_INVALID_ARGUMENT, "gT must be 16-byte aligned");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (!workspace || reinterpret_cast<uintptr_t>(workspace) % kAlign != 0 ||
+        workspace_bytes < ffi_forward_bce_workspace_bytes(B, N, L, K, x_transposed, dtype))
+        return fail(FFI_ERR_WORKSPACE, "ffi_forward_bce needs %zu bytes of %zu-byte aligned workspace",
+                    ffi_forward_bce_workspace_bytes(B, N, L, K, x_transposed, dtype), kAlign);
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    double* partials = reinterpret_cast<double*>(ws);
+    float* xws = reinterpret_cast<float*>(ws + align_up(kBcePartialBytes));
+
+    const bool smem = forward_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
+    const XPlan xp = plan_x(smem, B, N, x_transposed);
+    const float* xT = nullptr;
+    rc = stage_x(xp, static_cast<const float*>(x), xws, B, N, x_transposed, stream, &xT);
+    if (rc != FFI_OK) return rc;
+    FwdArgs a;
+    a.xT = xT;
+    a.ldx = xp.ld;
+    a.idx = idx;
+    a.W = static_cast<const float*>(W);
+    a.bias = bias;
+    a.y = nullptr;
+    a.B = static_cast<int>(B);
+    a.N = static_cast<int>(N);
+    a.L = static_cast<int>(L);
+    a.K = static_cast<int>(K);
+    const float scale = static_cast<float>(1.0 / (static_cast<double>(B) * static_cast<double>(L_total)));
+    const int64_t ldg = transposed_g_stride(B);
+    int ctas = 0;
+    bool handled = false;
+    rc = launch_forward_bce_stream(a, gT, ldg, scale, partials, &ctas, stream, &handled);
+    if (rc != FFI_OK) return rc;
+    if (!handled)
+        return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_bce covers K %% 4 == 0 with x resident in shared memory; "
+                                         "use ffi_forward + ffi_bce_grad for this shape");
+    if (static_cast<size_t>(ctas) * sizeof(double) > kBcePartialBytes)
+        return fail(FFI_ERR_UNSUPPORTED, "too many loss partials (%d)", ctas);
+    return launch_bce_positive_fix(xT, xp.ld, idx, a.W, bias, row_ptr, labels, gT, ldg, loss, partials, ctas, scale,
+                                   static_cast<int>(B), L, static_cast<int>(K), label_offset, stream);
 }

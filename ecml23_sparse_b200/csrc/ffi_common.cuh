@@ -99,6 +99,8 @@ int64_t transposed_g_stride(int64_t B);
 // column sums grad_bias[o] = sum_b g[b,o].
 int launch_transpose_g(const float* g, float* gT, float* gbias, int B, int64_t L, int64_t ldg,
                        cudaStream_t stream);
+// gbias[o] = sum_b gT[o][b]
+int launch_bias_grad_rows(const float* gT, int64_t ldg, int64_t L, float* gbias, cudaStream_t stream);
 
 // x [B,N] -> xT [N][ldx] (zero padded to ldx), fp32.
 int launch_transpose_pad(const float* src, float* dst, int rows, int cols, int64_t ld_dst,

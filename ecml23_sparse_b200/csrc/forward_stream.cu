@@ -24,9 +24,19 @@ struct FwdStreamParams {
     const float* bias;
     float* y;
     int B, N, L, K;
+    // fused sigmoid-BCE epilogue (BCE variant): instead of y the kernel writes the loss gradient,
+    // already transposed, gT[o][b] = scale * sigmoid(z[b,o]) (positives are corrected afterwards),
+    // and one partial sum of softplus(z) per CTA
+    float* gT;
+    long long ldg;
+    float scale;
+    double* loss_partials;
 };
 
-template <int BPL>
+__device__ __forceinline__ float softplus_dev(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float sigmoid_dev(float z) { return 1.f / (1.f + expf(-z)); }
+
+template <int BPL, bool BCE>
 __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_stream_kernel(FwdStreamParams p) {
     constexpr int BT = 32 * BPL;
     constexpr int S = BT + 8;  // result-tile row stride: conflict-free for both access patterns
@@ -88,6 +98,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_stream_kernel(FwdStreamPa
     long long q = gw;
     if (q < numQuads) issue(2 * q, 0);
     int s = 0;
+    float loss_local = 0.f;  // BCE: sum of softplus(z) over this lane's (b, o) pairs
     for (; q < numQuads; q += GW) {
 #pragma unroll
         for (int half = 0; half < 2; ++half, ++s) {
@@ -137,31 +148,65 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_stream_kernel(FwdStreamPa
                         accB[j] = fmaf(wB.w, vec_get(c3, j), accB[j]);
                     }
                 }
+                if constexpr (BCE) {
+                    // lanes hold consecutive batch elements: each (row, j) is one coalesced 128-byte store
 #pragma unroll
-                for (int j = 0; j < BPL; ++j) {
-                    ys[(2 * half) * S + lane + 32 * j] = accA[j] + biasA;
-                    ys[(2 * half + 1) * S + lane + 32 * j] = accB[j] + biasB;
+                    for (int j = 0; j < BPL; ++j) {
+                        const int b = b0 + lane + 32 * j;
+                        const bool live = b < p.B;
+                        const float zA = accA[j] + biasA, zB = accB[j] + biasB;
+                        if (live) loss_local += softplus_dev(zA) + (validB ? softplus_dev(zB) : 0.f);
+                        if (b < p.ldg) {
+                            p.gT[static_cast<size_t>(oA) * p.ldg + b] = live ? p.scale * sigmoid_dev(zA) : 0.f;
+                            if (validB) p.gT[static_cast<size_t>(oA + 1) * p.ldg + b] = live ? p.scale * sigmoid_dev(zB) : 0.f;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < BPL; ++j) {
+                        ys[(2 * half) * S + lane + 32 * j] = accA[j] + biasA;
+                        ys[(2 * half + 1) * S + lane + 32 * j] = accB[j] + biasB;
+                    }
                 }
             }
             __syncwarp();  // buffer `buf` may be overwritten by the next issue; ys rows are visible
         }
-        // Write out rows 4q .. 4q+3: lane = (batch row, output) -> 16-byte runs along o.
-        const long long oq = 4 * q;
+        if constexpr (!BCE) {
+            // Write out rows 4q .. 4q+3: lane = (batch row, output) -> 16-byte runs along o.
+            const long long oq = 4 * q;
 #pragma unroll
-        for (int it = 0; it < BT * 4 / 32; ++it) {
-            const int id = it * 32 + lane;
-            const int bl = id >> 2, oo = id & 3;
-            if (b0 + bl < p.B && oq + oo < L)
-                p.y[static_cast<size_t>(b0 + bl) * L + oq + oo] = ys[oo * S + bl];
+            for (int it = 0; it < BT * 4 / 32; ++it) {
+                const int id = it * 32 + lane;
+                const int bl = id >> 2, oo = id & 3;
+                if (b0 + bl < p.B && oq + oo < L)
+                    p.y[static_cast<size_t>(b0 + bl) * L + oq + oo] = ys[oo * S + bl];
+            }
+            __syncwarp();  // ys is rewritten by the next quad
         }
-        __syncwarp();  // ys is rewritten by the next quad
     }
     __pipeline_wait_prior(0);
+
+    if constexpr (BCE) {
+        // CTA partial of the loss sum in a fixed order: lanes (tree), then warps (serial).
+        double v = static_cast<double>(loss_local);
+#pragma unroll
+        for (int off = 16; off >= 1; off /= 2) v += __shfl_xor_sync(0xffffffffu, v, off);
+        __syncthreads();  // every warp is done with its shared-memory region
+        double* red = reinterpret_cast<double*>(smem_raw);
+        if (lane == 0) red[warp] = v;
+        __syncthreads();
+        if (tid == 0) {
+            double t = 0.0;
+            for (int w = 0; w < kWarps; ++w) t += red[w];
+            p.loss_partials[static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x] = t;
+        }
+    }
 }
 
-template <int BPL>
-int launch_stream_t(const FwdStreamParams& p, size_t smem, int nBT, const DeviceInfo& dev, cudaStream_t stream) {
-    auto kern = ffi_fwd_stream_kernel<BPL>;
+template <int BPL, bool BCE>
+int launch_stream_t(const FwdStreamParams& p, size_t smem, int nBT, const DeviceInfo& dev, cudaStream_t stream,
+                    int* ctas_out) {
+    auto kern = ffi_fwd_stream_kernel<BPL, BCE>;
     FFI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     int occ = 0;
     FFI_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kThreads, smem));
@@ -171,6 +216,7 @@ int launch_stream_t(const FwdStreamParams& p, size_t smem, int nBT, const Device
     const long long numQuads = (static_cast<long long>(p.L) + 3) / 4;
     const long long want = (numQuads + kWarps - 1) / kWarps;
     dim3 grid(static_cast<unsigned>(want < per_bt ? want : per_bt), static_cast<unsigned>(nBT));
+    if (ctas_out) *ctas_out = static_cast<int>(grid.x * grid.y);
     kern<<<grid, kThreads, smem, stream>>>(p);
     FFI_LAUNCH_CHECK("ffi_fwd_stream_kernel");
     return FFI_OK;
@@ -178,8 +224,16 @@ int launch_stream_t(const FwdStreamParams& p, size_t smem, int nBT, const Device
 
 }  // namespace
 
-// Launches the barrier-free kernel when the shape allows it; *handled tells the caller.
-int launch_forward_stream(const FwdArgs& a, cudaStream_t stream, bool* handled) {
+// Shared launcher: BCE epilogue when bce != nullptr.
+struct BceEpilogue {
+    float* gT;
+    long long ldg;
+    float scale;
+    double* loss_partials;
+    int* ctas;  // out: number of CTAs = number of loss partials written
+};
+
+static int launch_forward_stream_impl(const FwdArgs& a, const BceEpilogue* bce, cudaStream_t stream, bool* handled) {
     *handled = false;
     DeviceInfo dev;
     int rc = get_device_info(&dev);
@@ -205,11 +259,34 @@ int launch_forward_stream(const FwdArgs& a, cudaStream_t stream, bool* handled) 
     p.N = a.N;
     p.L = a.L;
     p.K = a.K;
+    p.gT = bce ? bce->gT : nullptr;
+    p.ldg = bce ? bce->ldg : 0;
+    p.scale = bce ? bce->scale : 0.f;
+    p.loss_partials = bce ? bce->loss_partials : nullptr;
     const int nBT = static_cast<int>(ceil_div(a.B, 32 * bpl));
     *handled = true;
-    if (bpl == 4) return launch_stream_t<4>(p, smem, nBT, dev, stream);
-    if (bpl == 2) return launch_stream_t<2>(p, smem, nBT, dev, stream);
-    return launch_stream_t<1>(p, smem, nBT, dev, stream);
+    if (bce) {
+        if (bpl == 4) return launch_stream_t<4, true>(p, smem, nBT, dev, stream, bce->ctas);
+        if (bpl == 2) return launch_stream_t<2, true>(p, smem, nBT, dev, stream, bce->ctas);
+        return launch_stream_t<1, true>(p, smem, nBT, dev, stream, bce->ctas);
+    }
+    if (bpl == 4) return launch_stream_t<4, false>(p, smem, nBT, dev, stream, nullptr);
+    if (bpl == 2) return launch_stream_t<2, false>(p, smem, nBT, dev, stream, nullptr);
+    return launch_stream_t<1, false>(p, smem, nBT, dev, stream, nullptr);
+}
+
+// Launches the barrier-free kernel when the shape allows it; *handled tells the caller.
+int launch_forward_stream(const FwdArgs& a, cudaStream_t stream, bool* handled) {
+    return launch_forward_stream_impl(a, nullptr, stream, handled);
+}
+
+// Forward with the fused sigmoid-BCE epilogue: writes gT[o][b] = scale * sigmoid(z[b,o]) (zero in the
+// padded batch columns) and one partial of sum softplus(z) per CTA; *ctas receives their number
+// (at most 2 * SM count).  *handled is false when the shape needs the unfused path.
+int launch_forward_bce_stream(const FwdArgs& a, float* gT, int64_t ldg, float scale, double* loss_partials, int* ctas,
+                              cudaStream_t stream, bool* handled) {
+    BceEpilogue e{gT, ldg, scale, loss_partials, ctas};
+    return launch_forward_stream_impl(a, &e, stream, handled);
 }
 
 }  // namespace ffi

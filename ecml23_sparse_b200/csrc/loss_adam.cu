@@ -103,6 +103,58 @@ __global__ void bce_finalize_kernel(const int* __restrict__ row_ptr, const int* 
     }
 }
 
+// After the forward kernel with the fused BCE epilogue: corrects gT at the positives
+// (g[b,o] = scale * (sigmoid(z) - 1) there), recomputing z of the few positive (b,o) pairs, and
+// finishes the loss = scale * (sum of CTA partials of softplus(z) - sum of z over the positives).
+// One block; all sums in a fixed order.
+__global__ void __launch_bounds__(256) bce_positive_fix_kernel(
+    const float* __restrict__ xT, long long ldx, const int* __restrict__ idx, const float* __restrict__ W,
+    const float* __restrict__ bias, const int* __restrict__ row_ptr, const int* __restrict__ labels,
+    float* __restrict__ gT, long long ldg, float* __restrict__ loss, const double* __restrict__ partials,
+    int nPartials, float scale, int B, long long L, int K, long long label_offset) {
+    __shared__ double sh[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    double possum = 0.0;  // kept by lane 0 of each warp
+    for (int b = 0; b < B; ++b) {
+        const int lo = row_ptr[b], hi = row_ptr[b + 1];
+        for (int e = lo + warp; e < hi; e += nwarps) {
+            const long long o = static_cast<long long>(labels[e]) - label_offset;
+            if (o < 0 || o >= L) continue;
+            float z = 0.f;
+            for (int k = lane; k < K; k += 32) {
+                const int i = idx[o * K + k];
+                z = fmaf(W[o * K + k], xT[static_cast<size_t>(i) * ldx + b], z);
+            }
+#pragma unroll
+            for (int off = 16; off >= 1; off /= 2) z += __shfl_xor_sync(0xffffffffu, z, off);
+            if (lane == 0) {
+                z += bias ? bias[o] : 0.f;
+                possum += static_cast<double>(z);
+                gT[static_cast<size_t>(o) * ldg + b] -= scale;
+            }
+        }
+    }
+    if (!loss) return;
+    double s = 0.0;
+    for (int j = threadIdx.x; j < nPartials; j += blockDim.x) s += partials[j];
+    s -= (lane == 0 ? possum : 0.0);
+    const double t = block_sum(s, sh);
+    if (threadIdx.x == 0) *loss = static_cast<float>(t * static_cast<double>(scale));
+}
+
+// grad_bias[o] = sum_b gT[o][b]: one warp per row of the transposed gradient, fixed lane tree.
+__global__ void __launch_bounds__(256) bias_grad_rows_kernel(const float* __restrict__ gT, long long ldg,
+                                                             long long L, float* __restrict__ gbias) {
+    const int lane = threadIdx.x & 31;
+    const long long o = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (o >= L) return;
+    float s = 0.f;
+    for (long long b = lane; b < ldg; b += 32) s += gT[static_cast<size_t>(o) * ldg + b];
+#pragma unroll
+    for (int off = 16; off >= 1; off /= 2) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (lane == 0) gbias[o] = s;
+}
+
 template <bool BF16>
 __global__ void __launch_bounds__(256) adam_kernel(void* __restrict__ w_v, float* __restrict__ m,
                                                    float* __restrict__ v, const float* __restrict__ grad,
@@ -150,6 +202,24 @@ __global__ void __launch_bounds__(256) adam_kernel_f32x4(float4* __restrict__ w,
 }
 
 }  // namespace
+}  // namespace ffi
+
+namespace ffi {
+int launch_bce_positive_fix(const float* xT, int64_t ldx, const int* idx, const float* W, const float* bias,
+                            const int* row_ptr, const int* labels, float* gT, int64_t ldg, float* loss,
+                            const double* partials, int nPartials, float scale, int B, int64_t L, int K,
+                            int64_t label_offset, cudaStream_t stream) {
+    bce_positive_fix_kernel<<<1, 256, 0, stream>>>(xT, ldx, idx, W, bias, row_ptr, labels, gT, ldg, loss, partials,
+                                                   nPartials, scale, B, L, K, label_offset);
+    FFI_LAUNCH_CHECK("bce_positive_fix_kernel");
+    return FFI_OK;
+}
+
+int launch_bias_grad_rows(const float* gT, int64_t ldg, int64_t L, float* gbias, cudaStream_t stream) {
+    bias_grad_rows_kernel<<<static_cast<unsigned>(ceil_div(L, 8)), 256, 0, stream>>>(gT, ldg, L, gbias);
+    FFI_LAUNCH_CHECK("bias_grad_rows_kernel");
+    return FFI_OK;
+}
 }  // namespace ffi
 
 using namespace ffi;

@@ -54,5 +54,35 @@ class FFILayer(nn.Module):
         tp_in = inputs.t().contiguous()  # custom_layer.py:48
         return ops.ffi_matmul_tp(tp_in, self.lookup(), self.weights(), self.bias).contiguous()
 
+    # ---- rewiring (sparse/layer.py:62-86,236-237; sparse/custom_layer.py:20-43) -----------------
+    def rewire_candidates(self, fraction: float = 0.01) -> torch.Tensor:
+        """Flat positions selected by the reference's FixedFractionSelector (layer.py:62-86):
+        num_selected = round(fraction * connections); threshold = the num_selected-th smallest |w|;
+        every connection with |w| strictly below the threshold is selected."""
+        if not 0.0 <= fraction <= 1.0:
+            raise ValueError("fraction must lie in [0, 1]")
+        flat = self.kernel_weights.detach().abs().reshape(-1)
+        num_selected = int(round(fraction * flat.numel()))
+        if num_selected < 1:
+            return torch.empty(0, dtype=torch.long, device=flat.device)
+        threshold = torch.kthvalue(flat, num_selected).values
+        return torch.nonzero(flat < threshold).reshape(-1)
+
+    @torch.no_grad()
+    def rewire(self, fraction: float = 0.01, optimizer=None, param_index: int = 0, generator=None) -> torch.Tensor:
+        """One rewiring step as StratifiedRewireLayerV2._rewire does (custom_layer.py:32-43): the selected
+        connections get a new source drawn uniformly from [0, in_features); their weights are kept; the
+        optimizer's moments at those positions are zeroed (custom_layer.py:20-30).  The index table is
+        updated in place, so the cached transposed index is rebuilt on the next backward pass.
+        Returns the rewired flat positions."""
+        locations = self.rewire_candidates(fraction)
+        if locations.numel() == 0:
+            return locations
+        new_sources = torch.randint(0, self.in_features, (locations.numel(),), generator=generator, dtype=torch.int32)
+        self.kernel_indices[locations] = new_sources.to(self.kernel_indices.device)
+        if optimizer is not None:
+            optimizer.zero_moments(param_index, locations)
+        return locations
+
     def extra_repr(self) -> str:
         return f"in_features={self.in_features}, units={self.units}, fan_in={self.fan_in}, bias={self.bias is not None}"

@@ -165,13 +165,17 @@ def _forward(features, lookup, weights, bias, transposed: bool) -> torch.Tensor:
 
 
 def _backward(features, lookup, weights, out_grad, transposed: bool, plan: Optional[FFIPlan] = None,
-              want_feature_grad=True, want_weight_grad=True, want_bias_grad=False):
+              want_feature_grad=True, want_weight_grad=True, want_bias_grad=False, grad_is_transposed=False):
+    """grad_is_transposed: `out_grad` is gT[L][ldg] (from forward_bce / transpose_gradient), not g[B,L]."""
     features = _check_cuda("features", features, (torch.float32,))
     weights = _check_cuda("weights", weights, (torch.float32,))
     out_grad = _check_cuda("out_grad", out_grad, (torch.float32,))
     lookup = _as_index(lookup)
     B, N, L, K = _shapes(features, lookup, weights, transposed)
-    if tuple(out_grad.shape) != (B, L):
+    if grad_is_transposed:
+        if out_grad.shape[0] != L or out_grad.shape[1] < B:
+            raise ValueError(f"transposed out_grad has shape {tuple(out_grad.shape)}, expected [{L}, >= {B}]")
+    elif tuple(out_grad.shape) != (B, L):
         raise ValueError(f"out_grad has shape {tuple(out_grad.shape)}, expected {(B, L)}")
     lib = _lib.load()
     dev = features.device
@@ -191,12 +195,49 @@ def _backward(features, lookup, weights, out_grad, transposed: bool, plan: Optio
             off = (-ws.data_ptr()) % 256
             ws_ptr = ws.data_ptr() + off
             ws_len = ws.numel() - off
-        _lib.check(lib.ffi_backward(features.data_ptr(), lookup.data_ptr(), weights.data_ptr(), out_grad.data_ptr(),
-                                    handle, gx.data_ptr() if gx is not None else None,
-                                    gw.data_ptr() if gw is not None else None,
-                                    gb.data_ptr() if gb is not None else None,
-                                    B, N, L, K, int(transposed), _lib.FFI_F32, ws_ptr, ws_len, _stream_ptr(dev)))
+        outs = (gx.data_ptr() if gx is not None else None, gw.data_ptr() if gw is not None else None,
+                gb.data_ptr() if gb is not None else None)
+        if grad_is_transposed:
+            _lib.check(lib.ffi_backward_from_transposed(features.data_ptr(), lookup.data_ptr(), weights.data_ptr(),
+                                                        out_grad.data_ptr(), out_grad.shape[1], handle, *outs,
+                                                        B, N, L, K, int(transposed), _lib.FFI_F32, ws_ptr, ws_len,
+                                                        _stream_ptr(dev)))
+        else:
+            _lib.check(lib.ffi_backward(features.data_ptr(), lookup.data_ptr(), weights.data_ptr(), out_grad.data_ptr(),
+                                        handle, *outs, B, N, L, K, int(transposed), _lib.FFI_F32, ws_ptr, ws_len,
+                                        _stream_ptr(dev)))
     return gx, gw, gb
+
+
+def forward_bce(features, lookup, weights, bias, row_ptr, labels, transposed: bool, total_labels=None,
+                label_offset: int = 0):
+    """Forward with the fused sigmoid-BCE gradient: returns (loss scalar tensor, gT[L][ldg]).
+
+    The logits are never materialised.  Raises FFIError (FFI_ERR_UNSUPPORTED) for shapes the fused
+    kernel does not cover; use `_forward` + `sparse_bce_with_logits` there."""
+    features = _check_cuda("features", features, (torch.float32,))
+    weights = _check_cuda("weights", weights, (torch.float32,))
+    lookup = _as_index(lookup)
+    B, N, L, K = _shapes(features, lookup, weights, transposed)
+    dev = features.device
+    lib = _lib.load()
+    row_ptr = row_ptr.to(device=dev, dtype=torch.int32).contiguous()
+    labels = labels.to(device=dev, dtype=torch.int32).contiguous()
+    if row_ptr.numel() != B + 1:
+        raise ValueError("row_ptr must have B+1 entries")
+    ldg = int(lib.ffi_transposed_gradient_stride(B))
+    gT = torch.empty((L, ldg), dtype=torch.float32, device=dev)
+    loss = torch.empty((), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        ws_bytes = lib.ffi_forward_bce_workspace_bytes(B, N, L, K, int(transposed), _lib.FFI_F32)
+        ws = _workspace(dev, ws_bytes + 256)
+        off = (-ws.data_ptr()) % 256
+        _lib.check(lib.ffi_forward_bce(features.data_ptr(), lookup.data_ptr(), weights.data_ptr(),
+                                       bias.data_ptr() if bias is not None else None, row_ptr.data_ptr(),
+                                       labels.data_ptr() if labels.numel() else row_ptr.data_ptr(), gT.data_ptr(),
+                                       loss.data_ptr(), B, N, L, K, total_labels or L, label_offset, int(transposed),
+                                       _lib.FFI_F32, ws.data_ptr() + off, ws.numel() - off, _stream_ptr(dev)))
+    return loss, gT
 
 
 def transpose_gradient(out_grad: torch.Tensor, want_bias_grad: bool = False):

@@ -134,6 +134,38 @@ int ffi_transpose_gradient(const float* g, float* gT, float* grad_bias, int64_t 
                            void* stream);
 
 /*
+ * ffi_backward for a caller that already holds the transposed gradient gT[L][ldg] (from
+ * ffi_forward_bce or ffi_transpose_gradient): no transposition pass.  grad_bias, when requested,
+ * is the row sum of gT.  Returns FFI_ERR_UNSUPPORTED for the few shapes whose grad_W kernel
+ * needs g[B,L] itself (K not a multiple of 4 together with a batch above 128 or wide N).
+ */
+int ffi_backward_from_transposed(const void* x, const int32_t* idx, const void* W, const float* gT,
+                                 int64_t ldg, const ffi_plan* plan, float* grad_x, float* grad_w,
+                                 float* grad_bias, int64_t B, int64_t N, int64_t L, int64_t K,
+                                 int x_transposed, int dtype, void* workspace, size_t workspace_bytes,
+                                 void* stream);
+
+/*
+ * Forward pass with the sigmoid-BCE gradient fused into its epilogue: the B*L logits are never
+ * written.  Output: gT[L][ldg] (ldg = ffi_transposed_gradient_stride(B)) with
+ *   gT[o][b] = (sigmoid(z[b,o]) - t[b,o]) / (B * L_total),  z = FFI(x) + bias,
+ * zero in the padded batch columns, ready for ffi_backward_from_transposed; *loss (device float,
+ * may be NULL) receives the mean BCE over B*L_total.  Targets as in ffi_bce_grad (CSR, labels of
+ * one row distinct; L_total / label_offset describe a label shard).  Replaces the chain
+ * FanInSparseMatmulTp -> bias_add -> SparseBinaryCrossEntropyLoss -> its gradient
+ * (sparse/custom_layer.py:45-50, sparse/layer.py:245-247, sparse/metrics.py:132-139,167-173).
+ * Covers K % 4 == 0 with the x tile resident in shared memory; other shapes return
+ * FFI_ERR_UNSUPPORTED (use ffi_forward + ffi_bce_grad).  Workspace: 256-byte aligned,
+ * ffi_forward_bce_workspace_bytes bytes.
+ */
+size_t ffi_forward_bce_workspace_bytes(int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed,
+                                       int dtype);
+int ffi_forward_bce(const void* x, const int32_t* idx, const void* W, const float* bias,
+                    const int32_t* row_ptr, const int32_t* labels, float* gT, float* loss, int64_t B,
+                    int64_t N, int64_t L, int64_t K, int64_t L_total, int64_t label_offset,
+                    int x_transposed, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * grad_x without any allocation and without a caller workspace.  This entry point has no
  * counterpart in the reference.
  *

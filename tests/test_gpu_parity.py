@@ -329,3 +329,56 @@ def test_headline_shape_full_size(cuda_device):
     # determinism at full size
     gx2, gW2 = ffi.fan_in_sparse_matmul_grad_tp(xT, idx, W, g)
     assert torch.equal(gx, gx2) and torch.equal(gW, gW2)
+
+
+def test_transpose_gradient_and_backward_from_transposed(cuda_device):
+    dev = cuda_device
+    from ecml23_sparse_b200 import ops
+    for shape in [(128, 768, 5_001, 32), (37, 254, 513, 16), (200, 100, 300, 8)]:
+        B, N, L, K = shape
+        x, idx, W, g = reference_style_inputs(shape, seed=3, relu_grad=False)
+        gT, gb = ops.transpose_gradient(to_cuda(g, dev), want_bias_grad=True)
+        assert gT.shape[0] == L and gT.shape[1] >= B and gT.shape[1] % 32 == 0
+        assert torch.equal(gT[:, :B], to_cuda(g, dev).t())
+        assert not gT[:, B:].any()
+        assert_close(gb.cpu().numpy(), oracle.grad_bias_f64(g), RTOL, ATOL, "grad_bias from transposition")
+        args = (to_cuda(x, dev), to_cuda(idx, dev), to_cuda(W, dev))
+        gx1, gw1, gb1 = ops._backward(*args, to_cuda(g, dev), False, want_bias_grad=True)
+        gx2, gw2, gb2 = ops._backward(*args, gT, False, want_bias_grad=True, grad_is_transposed=True)
+        assert torch.equal(gx1, gx2) and torch.equal(gw1, gw2)
+        assert_close(gb2.cpu().numpy(), oracle.grad_bias_f64(g), RTOL, ATOL, "grad_bias from gT rows")
+
+
+@pytest.mark.parametrize("shape,transposed", [((128, 768, 20_011, 32), True), ((37, 254, 513, 16), False),
+                                              ((64, 100, 1000, 8), True)], ids=["headline-like", "small", "b64"])
+def test_fused_forward_bce_matches_unfused(cuda_device, shape, transposed):
+    dev = cuda_device
+    from ecml23_sparse_b200 import ops
+    B, N, L, K = shape
+    x, idx, W, _ = config_style_inputs(B, N, L, K, seed=9)
+    bias = synth.normal(9, 40, (L,), std=0.5).numpy()
+    row_ptr, labels = synth.multi_hot_targets(9, 41, B, L)
+    xin = np.ascontiguousarray(x.T) if transposed else x
+    loss, gT = ops.forward_bce(to_cuda(xin, dev), to_cuda(idx, dev), to_cuda(W, dev), to_cuda(bias, dev), row_ptr,
+                               labels, transposed)
+    z = oracle.forward_f64(x, idx, W, bias=bias).astype(np.float32)
+    loss_ref, g_ref = oracle.bce_f64(z, row_ptr.numpy(), labels.numpy())
+    assert abs(float(loss) - loss_ref) <= 2e-5 * abs(loss_ref) + 1e-7
+    assert_close(gT[:, :B].t().cpu().numpy(), g_ref, 5e-5, 1e-12, "fused BCE gradient")
+    assert not gT[:, B:].any()
+    # label shard [lo, hi) of the same problem
+    lo, hi = L // 4, L // 4 + (L // 2) // 4 * 4
+    loss_s, gT_s = ops.forward_bce(to_cuda(xin, dev), to_cuda(idx[lo:hi], dev), to_cuda(W[lo:hi], dev),
+                                   to_cuda(bias[lo:hi], dev), row_ptr, labels, transposed, total_labels=L,
+                                   label_offset=lo)
+    assert_close(gT_s[:, :B].t().cpu().numpy(), g_ref[:, lo:hi], 5e-5, 1e-12, "fused BCE gradient (shard)")
+
+
+def test_fused_forward_bce_reports_unsupported_shapes(cuda_device):
+    dev = cuda_device
+    from ecml23_sparse_b200 import ops
+    x, idx, W, _ = reference_style_inputs((17, 12, 63, 44 + 1))  # K = 45 is not a multiple of 4
+    row_ptr, labels = synth.multi_hot_targets(1, 2, 17, 63)
+    with pytest.raises(_lib.FFIError) as e:
+        ops.forward_bce(to_cuda(x, dev), to_cuda(idx, dev), to_cuda(W, dev), None, row_ptr, labels, False)
+    assert e.value.status == 2
