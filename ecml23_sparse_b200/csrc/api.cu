@@ -340,14 +340,15 @@ int launch_forward_bce_stream(const FwdArgs& a, float* gT, int64_t ldg, float sc
                               cudaStream_t stream, bool* handled);
 int launch_bce_positive_fix(const float* xT, int64_t ldx, const int* idx, const float* W, const float* bias,
                             const int* row_ptr, const int* labels, float* gT, int64_t ldg, float* loss,
-                            const double* partials, int nPartials, float scale, int B, int64_t L, int K,
-                            int64_t label_offset, cudaStream_t stream);
+                            const double* partials, int nPartials, double* pos_partials, float scale, int B,
+                            int64_t L, int K, int64_t label_offset, cudaStream_t stream);
 constexpr size_t kBcePartialBytes = 1024 * sizeof(double);  // >= one partial per CTA of the forward kernel
 }  // namespace ffi
 
 extern "C" size_t ffi_forward_bce_workspace_bytes(int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed,
                                                   int dtype) {
-    return ffi_forward_workspace_bytes(B, N, L, K, x_transposed, dtype) + kAlign + kBcePartialBytes;
+    return ffi_forward_workspace_bytes(B, N, L, K, x_transposed, dtype) + 2 * kAlign + kBcePartialBytes +
+           static_cast<size_t>(B > 0 ? B : 0) * sizeof(double);
 }
 
 extern "C" int ffi_forward_bce(const void* x, const int32_t* idx, const void* W, const float* bias,
@@ -368,7 +369,8 @@ extern "C" int ffi_forward_bce(const void* x, const int32_t* idx, const void* W,
                     ffi_forward_bce_workspace_bytes(B, N, L, K, x_transposed, dtype), kAlign);
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     double* partials = reinterpret_cast<double*>(ws);
-    float* xws = reinterpret_cast<float*>(ws + align_up(kBcePartialBytes));
+    double* pos_partials = reinterpret_cast<double*>(ws + align_up(kBcePartialBytes));
+    float* xws = reinterpret_cast<float*>(ws + align_up(kBcePartialBytes) + align_up(static_cast<size_t>(B) * sizeof(double)));
 
     const bool smem = forward_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
     const XPlan xp = plan_x(smem, B, N, x_transposed);
@@ -397,6 +399,6 @@ extern "C" int ffi_forward_bce(const void* x, const int32_t* idx, const void* W,
                                          "use ffi_forward + ffi_bce_grad for this shape");
     if (static_cast<size_t>(ctas) * sizeof(double) > kBcePartialBytes)
         return fail(FFI_ERR_UNSUPPORTED, "too many loss partials (%d)", ctas);
-    return launch_bce_positive_fix(xT, xp.ld, idx, a.W, bias, row_ptr, labels, gT, ldg, loss, partials, ctas, scale,
-                                   static_cast<int>(B), L, static_cast<int>(K), label_offset, stream);
+    return launch_bce_positive_fix(xT, xp.ld, idx, a.W, bias, row_ptr, labels, gT, ldg, loss, partials, ctas,
+                                   pos_partials, scale, static_cast<int>(B), L, static_cast<int>(K), label_offset, stream);
 }

@@ -104,40 +104,51 @@ __global__ void bce_finalize_kernel(const int* __restrict__ row_ptr, const int* 
 }
 
 // After the forward kernel with the fused BCE epilogue: corrects gT at the positives
-// (g[b,o] = scale * (sigmoid(z) - 1) there), recomputing z of the few positive (b,o) pairs, and
-// finishes the loss = scale * (sum of CTA partials of softplus(z) - sum of z over the positives).
-// One block; all sums in a fixed order.
+// (g[b,o] = scale * (sigmoid(z) - 1) there), recomputing z of the few positive (b,o) pairs.
+// One block per sample; pos_partials[b] = sum of z over the sample's positives (fixed order).
 __global__ void __launch_bounds__(256) bce_positive_fix_kernel(
     const float* __restrict__ xT, long long ldx, const int* __restrict__ idx, const float* __restrict__ W,
     const float* __restrict__ bias, const int* __restrict__ row_ptr, const int* __restrict__ labels,
-    float* __restrict__ gT, long long ldg, float* __restrict__ loss, const double* __restrict__ partials,
-    int nPartials, float scale, int B, long long L, int K, long long label_offset) {
+    float* __restrict__ gT, long long ldg, double* __restrict__ pos_partials, float scale, long long L, int K,
+    long long label_offset) {
     __shared__ double sh[32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int b = blockIdx.x;
     double possum = 0.0;  // kept by lane 0 of each warp
-    for (int b = 0; b < B; ++b) {
-        const int lo = row_ptr[b], hi = row_ptr[b + 1];
-        for (int e = lo + warp; e < hi; e += nwarps) {
-            const long long o = static_cast<long long>(labels[e]) - label_offset;
-            if (o < 0 || o >= L) continue;
-            float z = 0.f;
-            for (int k = lane; k < K; k += 32) {
-                const int i = idx[o * K + k];
-                z = fmaf(W[o * K + k], xT[static_cast<size_t>(i) * ldx + b], z);
-            }
+    const int lo = row_ptr[b], hi = row_ptr[b + 1];
+    for (int e = lo + warp; e < hi; e += nwarps) {
+        const long long o = static_cast<long long>(labels[e]) - label_offset;
+        if (o < 0 || o >= L) continue;
+        float z = 0.f;
+        for (int k = lane; k < K; k += 32) {
+            const int i = idx[o * K + k];
+            z = fmaf(W[o * K + k], xT[static_cast<size_t>(i) * ldx + b], z);
+        }
 #pragma unroll
-            for (int off = 16; off >= 1; off /= 2) z += __shfl_xor_sync(0xffffffffu, z, off);
-            if (lane == 0) {
-                z += bias ? bias[o] : 0.f;
-                possum += static_cast<double>(z);
-                gT[static_cast<size_t>(o) * ldg + b] -= scale;
-            }
+        for (int off = 16; off >= 1; off /= 2) z += __shfl_xor_sync(0xffffffffu, z, off);
+        if (lane == 0) {
+            z += bias ? bias[o] : 0.f;
+            possum += static_cast<double>(z);
+            gT[static_cast<size_t>(o) * ldg + b] -= scale;
         }
     }
-    if (!loss) return;
+    if (lane == 0) sh[warp] = possum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < nwarps; ++w) t += sh[w];
+        pos_partials[b] = t;
+    }
+}
+
+// loss = scale * (sum of the forward kernel's CTA partials of softplus(z) - sum of z over the positives).
+__global__ void __launch_bounds__(256) bce_loss_finalize_kernel(const double* __restrict__ partials, int nPartials,
+                                                                const double* __restrict__ pos_partials, int B,
+                                                                float scale, float* __restrict__ loss) {
+    __shared__ double sh[32];
     double s = 0.0;
     for (int j = threadIdx.x; j < nPartials; j += blockDim.x) s += partials[j];
-    s -= (lane == 0 ? possum : 0.0);
+    for (int j = threadIdx.x; j < B; j += blockDim.x) s -= pos_partials[j];
     const double t = block_sum(s, sh);
     if (threadIdx.x == 0) *loss = static_cast<float>(t * static_cast<double>(scale));
 }
@@ -207,10 +218,11 @@ __global__ void __launch_bounds__(256) adam_kernel_f32x4(float4* __restrict__ w,
 namespace ffi {
 int launch_bce_positive_fix(const float* xT, int64_t ldx, const int* idx, const float* W, const float* bias,
                             const int* row_ptr, const int* labels, float* gT, int64_t ldg, float* loss,
-                            const double* partials, int nPartials, float scale, int B, int64_t L, int K,
-                            int64_t label_offset, cudaStream_t stream) {
-    bce_positive_fix_kernel<<<1, 256, 0, stream>>>(xT, ldx, idx, W, bias, row_ptr, labels, gT, ldg, loss, partials,
-                                                   nPartials, scale, B, L, K, label_offset);
+                            const double* partials, int nPartials, double* pos_partials, float scale, int B,
+                            int64_t L, int K, int64_t label_offset, cudaStream_t stream) {
+    bce_positive_fix_kernel<<<static_cast<unsigned>(B), 256, 0, stream>>>(xT, ldx, idx, W, bias, row_ptr, labels, gT,
+                                                                          ldg, pos_partials, scale, L, K, label_offset);
+    if (loss) bce_loss_finalize_kernel<<<1, 256, 0, stream>>>(partials, nPartials, pos_partials, B, scale, loss);
     FFI_LAUNCH_CHECK("bce_positive_fix_kernel");
     return FFI_OK;
 }
