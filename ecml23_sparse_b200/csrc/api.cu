@@ -50,6 +50,7 @@ int get_device_info(DeviceInfo* info) {
 }
 
 bool forward_uses_smem_x(int B, int N, int K, int* bpl_out);
+int launch_widen_bf16(const void* src, float* dst, int64_t n, cudaStream_t stream);
 bool grad_w_uses_smem_x(int B, int N, int K, int* bpl_out);
 
 namespace {
@@ -106,6 +107,33 @@ int stage_x(const XPlan& xp, const float* x, float* ws, int64_t B, int64_t N, in
     return FFI_OK;
 }
 
+// bf16 storage of x and W: both are widened to fp32 at the front of the workspace (exact), the
+// fp32 kernels then run on the copies with the rest of the workspace.
+size_t widen_bytes(int64_t B, int64_t N, int64_t L, int64_t K) {
+    return align_up(static_cast<size_t>(B) * N * 4) + align_up(static_cast<size_t>(L) * K * 4);
+}
+
+int widen_inputs(const void* x, const void* W, int64_t B, int64_t N, int64_t L, int64_t K, void* workspace,
+                 size_t workspace_bytes, cudaStream_t stream, const float** x32, const float** W32, void** rest,
+                 size_t* rest_bytes) {
+    const size_t need = widen_bytes(B, N, L, K);
+    if (!workspace || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % kAlign != 0)
+        return fail(FFI_ERR_WORKSPACE, "bf16 inputs need %zu bytes of %zu-byte aligned workspace for their fp32 copies",
+                    need, kAlign);
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    float* xd = reinterpret_cast<float*>(ws);
+    float* wd = reinterpret_cast<float*>(ws + align_up(static_cast<size_t>(B) * N * 4));
+    int rc = launch_widen_bf16(x, xd, B * N, stream);
+    if (rc != FFI_OK) return rc;
+    rc = launch_widen_bf16(W, wd, L * K, stream);
+    if (rc != FFI_OK) return rc;
+    *x32 = xd;
+    *W32 = wd;
+    *rest = ws + need;
+    *rest_bytes = workspace_bytes - need;
+    return FFI_OK;
+}
+
 }  // namespace
 }  // namespace ffi
 
@@ -117,9 +145,9 @@ extern "C" int ffi_version(void) { return 100; }
 
 extern "C" size_t ffi_forward_workspace_bytes(int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed,
                                               int dtype) {
-    if (check_shape(B, N, L, K) != FFI_OK || dtype != FFI_F32) return 0;
+    if (check_shape(B, N, L, K) != FFI_OK || (dtype != FFI_F32 && dtype != FFI_BF16)) return 0;
     const bool smem = forward_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
-    return plan_x(smem, B, N, x_transposed).bytes;
+    return plan_x(smem, B, N, x_transposed).bytes + (dtype == FFI_BF16 ? widen_bytes(B, N, L, K) : 0);
 }
 
 extern "C" int ffi_forward(const void* x, const int32_t* idx, const void* W, const float* bias, float* y,
@@ -128,8 +156,16 @@ extern "C" int ffi_forward(const void* x, const int32_t* idx, const void* W, con
     if (!x || !idx || !W || !y) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_forward");
     int rc = check_shape(B, N, L, K);
     if (rc != FFI_OK) return rc;
-    if (dtype != FFI_F32) return fail(FFI_ERR_UNSUPPORTED, "ffi_forward: dtype %d not supported", dtype);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (dtype == FFI_BF16) {
+        const float *x32 = nullptr, *W32 = nullptr;
+        void* rest = nullptr;
+        size_t rest_bytes = 0;
+        rc = widen_inputs(x, W, B, N, L, K, workspace, workspace_bytes, stream, &x32, &W32, &rest, &rest_bytes);
+        if (rc != FFI_OK) return rc;
+        return ffi_forward(x32, idx, W32, bias, y, B, N, L, K, x_transposed, FFI_F32, rest, rest_bytes, stream_v);
+    }
+    if (dtype != FFI_F32) return fail(FFI_ERR_UNSUPPORTED, "ffi_forward: dtype %d not supported", dtype);
 
     const bool smem = forward_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
     const XPlan xp = plan_x(smem, B, N, x_transposed);
@@ -168,8 +204,8 @@ extern "C" int ffi_transpose_gradient(const float* g, float* gT, float* grad_bia
 
 extern "C" size_t ffi_backward_workspace_bytes(const ffi_plan* plan, int64_t B, int64_t N, int64_t L, int64_t K,
                                                int x_transposed, int dtype, int want_grad_x, int want_grad_w) {
-    if (check_shape(B, N, L, K) != FFI_OK || dtype != FFI_F32) return 0;
-    size_t total = 0;
+    if (check_shape(B, N, L, K) != FFI_OK || (dtype != FFI_F32 && dtype != FFI_BF16)) return 0;
+    size_t total = dtype == FFI_BF16 ? widen_bytes(B, N, L, K) : 0;
     if (want_grad_w) {
         const bool smem = grad_w_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
         total += plan_x(smem, B, N, x_transposed).bytes;
@@ -193,6 +229,16 @@ static int backward_impl(const void* x, const int32_t* idx, const void* W, const
     if (!x || !idx || !W || (!g && !gT_in)) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_backward");
     int rc = check_shape(B, N, L, K);
     if (rc != FFI_OK) return rc;
+    if (dtype == FFI_BF16) {
+        const float *x32 = nullptr, *W32 = nullptr;
+        void* rest = nullptr;
+        size_t rest_bytes = 0;
+        rc = widen_inputs(x, W, B, N, L, K, workspace, workspace_bytes, static_cast<cudaStream_t>(stream_v), &x32, &W32,
+                          &rest, &rest_bytes);
+        if (rc != FFI_OK) return rc;
+        return backward_impl(x32, idx, W32, g, gT_in, ldg_in, plan, grad_x, grad_w, grad_bias, B, N, L, K, x_transposed,
+                             FFI_F32, rest, rest_bytes, stream_v);
+    }
     if (dtype != FFI_F32) return fail(FFI_ERR_UNSUPPORTED, "ffi_backward: dtype %d not supported", dtype);
     if (grad_x) {
         if (!plan) return fail(FFI_ERR_INVALID_ARGUMENT, "grad_x needs a plan (ffi_plan_create)");

@@ -216,6 +216,24 @@ __global__ void __launch_bounds__(256) adam_kernel_f32x4(float4* __restrict__ w,
 }  // namespace ffi
 
 namespace ffi {
+namespace {
+__global__ void __launch_bounds__(256) widen_bf16_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst,
+                                                         long long n) {
+    const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long e = tid; e < n; e += stride) dst[e] = __bfloat162float(src[e]);
+}
+}  // namespace
+
+// bf16 -> fp32 (exact).
+int launch_widen_bf16(const void* src, float* dst, int64_t n, cudaStream_t stream) {
+    const long long blocks = (n + 255) / 256;
+    widen_bf16_kernel<<<static_cast<unsigned>(blocks < 1184 * 4 ? (blocks < 1 ? 1 : blocks) : 1184 * 4), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(src), dst, n);
+    FFI_LAUNCH_CHECK("widen_bf16_kernel");
+    return FFI_OK;
+}
+
 int launch_bce_positive_fix(const float* xT, int64_t ldx, const int* idx, const float* W, const float* bias,
                             const int* row_ptr, const int* labels, float* gT, int64_t ldg, float* loss,
                             const double* partials, int nPartials, double* pos_partials, float scale, int B,

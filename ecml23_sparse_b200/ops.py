@@ -141,9 +141,20 @@ def clear_caches():
     _workspaces.clear()
 
 
+_STORAGE_DTYPES = (torch.float32, torch.bfloat16)
+
+
+def _storage_dtype(features, weights) -> int:
+    """x and W share one storage type: fp32, or bf16 (accumulation, y and all gradients stay fp32)."""
+    if features.dtype != weights.dtype:
+        raise TypeError(f"features ({features.dtype}) and weights ({weights.dtype}) must have the same dtype")
+    return _lib.FFI_BF16 if features.dtype == torch.bfloat16 else _lib.FFI_F32
+
+
 def _forward(features, lookup, weights, bias, transposed: bool) -> torch.Tensor:
-    features = _check_cuda("features", features, (torch.float32,))
-    weights = _check_cuda("weights", weights, (torch.float32,))
+    features = _check_cuda("features", features, _STORAGE_DTYPES)
+    weights = _check_cuda("weights", weights, _STORAGE_DTYPES)
+    dtype = _storage_dtype(features, weights)
     lookup = _as_index(lookup)
     B, N, L, K = _shapes(features, lookup, weights, transposed)
     lib = _lib.load()
@@ -154,21 +165,24 @@ def _forward(features, lookup, weights, bias, transposed: bool) -> torch.Tensor:
         bias = bias.contiguous()
     out = torch.empty((B, L), dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
-        ws_bytes = lib.ffi_forward_workspace_bytes(B, N, L, K, int(transposed), _lib.FFI_F32)
-        ws = _workspace(dev, ws_bytes)
+        ws_bytes = lib.ffi_forward_workspace_bytes(B, N, L, K, int(transposed), dtype)
+        ws = _workspace(dev, ws_bytes + 256 if ws_bytes else 0)
+        ws_ptr, ws_len = None, 0
+        if ws is not None:
+            off = (-ws.data_ptr()) % 256
+            ws_ptr, ws_len = ws.data_ptr() + off, ws.numel() - off
         _lib.check(lib.ffi_forward(features.data_ptr(), lookup.data_ptr(), weights.data_ptr(),
                                    bias.data_ptr() if bias is not None else None, out.data_ptr(),
-                                   B, N, L, K, int(transposed), _lib.FFI_F32,
-                                   ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
-                                   _stream_ptr(dev)))
+                                   B, N, L, K, int(transposed), dtype, ws_ptr, ws_len, _stream_ptr(dev)))
     return out
 
 
 def _backward(features, lookup, weights, out_grad, transposed: bool, plan: Optional[FFIPlan] = None,
               want_feature_grad=True, want_weight_grad=True, want_bias_grad=False, grad_is_transposed=False):
     """grad_is_transposed: `out_grad` is gT[L][ldg] (from forward_bce / transpose_gradient), not g[B,L]."""
-    features = _check_cuda("features", features, (torch.float32,))
-    weights = _check_cuda("weights", weights, (torch.float32,))
+    features = _check_cuda("features", features, _STORAGE_DTYPES)
+    weights = _check_cuda("weights", weights, _STORAGE_DTYPES)
+    dtype = _storage_dtype(features, weights)
     out_grad = _check_cuda("out_grad", out_grad, (torch.float32,))
     lookup = _as_index(lookup)
     B, N, L, K = _shapes(features, lookup, weights, transposed)
@@ -181,12 +195,12 @@ def _backward(features, lookup, weights, out_grad, transposed: bool, plan: Optio
     dev = features.device
     if want_feature_grad and plan is None:
         plan = get_plan(lookup, N)
-    gx = torch.empty_like(features) if want_feature_grad else None
-    gw = torch.empty_like(weights) if want_weight_grad else None
+    gx = torch.empty(features.shape, dtype=torch.float32, device=dev) if want_feature_grad else None
+    gw = torch.empty(weights.shape, dtype=torch.float32, device=dev) if want_weight_grad else None
     gb = torch.empty((L,), dtype=torch.float32, device=dev) if want_bias_grad else None
     with torch.cuda.device(dev):
         handle = plan.handle if plan is not None else None
-        ws_bytes = lib.ffi_backward_workspace_bytes(handle, B, N, L, K, int(transposed), _lib.FFI_F32,
+        ws_bytes = lib.ffi_backward_workspace_bytes(handle, B, N, L, K, int(transposed), dtype,
                                                     int(want_feature_grad), int(want_weight_grad or want_bias_grad))
         ws = _workspace(dev, ws_bytes + 256 if ws_bytes else 0)
         ws_ptr = None
@@ -200,11 +214,11 @@ def _backward(features, lookup, weights, out_grad, transposed: bool, plan: Optio
         if grad_is_transposed:
             _lib.check(lib.ffi_backward_from_transposed(features.data_ptr(), lookup.data_ptr(), weights.data_ptr(),
                                                         out_grad.data_ptr(), out_grad.shape[1], handle, *outs,
-                                                        B, N, L, K, int(transposed), _lib.FFI_F32, ws_ptr, ws_len,
+                                                        B, N, L, K, int(transposed), dtype, ws_ptr, ws_len,
                                                         _stream_ptr(dev)))
         else:
             _lib.check(lib.ffi_backward(features.data_ptr(), lookup.data_ptr(), weights.data_ptr(), out_grad.data_ptr(),
-                                        handle, *outs, B, N, L, K, int(transposed), _lib.FFI_F32, ws_ptr, ws_len,
+                                        handle, *outs, B, N, L, K, int(transposed), dtype, ws_ptr, ws_len,
                                         _stream_ptr(dev)))
     return gx, gw, gb
 

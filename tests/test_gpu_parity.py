@@ -382,3 +382,34 @@ def test_fused_forward_bce_reports_unsupported_shapes(cuda_device):
     with pytest.raises(_lib.FFIError) as e:
         ops.forward_bce(to_cuda(x, dev), to_cuda(idx, dev), to_cuda(W, dev), None, row_ptr, labels, False)
     assert e.value.status == 2
+
+
+@pytest.mark.parametrize("shape,transposed", [((64, 512, 3_001, 32), True), ((37, 254, 513, 16), False),
+                                              ((130, 100, 600, 73), False)], ids=["wiki-like", "small", "odd"])
+def test_bf16_storage_of_x_and_w(cuda_device, shape, transposed):
+    """x and W stored as bf16, fp32 accumulation (benchmark configurations 2-4; the reference is fp32
+    only, tfsparse/cc/kernels/register.cpp:79-109).  Inputs are rounded to bf16 once; the CUDA result
+    must match the fp64 oracle evaluated on the rounded values to fp32 accuracy, and stay within
+    rel 2e-2 (of the output scale) of the result for the unrounded fp32 inputs."""
+    dev = cuda_device
+    from ecml23_sparse_b200 import ops
+    B, N, L, K = shape
+    x, idx, W, g = config_style_inputs(B, N, L, K, seed=17)
+    xb = torch.from_numpy(x).to(torch.bfloat16)
+    Wb = torch.from_numpy(W).to(torch.bfloat16)
+    xr, Wr = xb.float().numpy(), Wb.float().numpy()          # the rounded values, exactly
+    xin = (xb.t().contiguous() if transposed else xb).to(dev)
+    y = ops._forward(xin, to_cuda(idx, dev), Wb.to(dev), None, transposed).cpu().numpy()
+    gx, gw, _ = ops._backward(xin, to_cuda(idx, dev), Wb.to(dev), to_cuda(g, dev), transposed)
+    assert gx.dtype == torch.float32 and gw.dtype == torch.float32
+    gx = gx.cpu().numpy().T if transposed else gx.cpu().numpy()
+    gw = gw.cpu().numpy()
+    assert_close(y, oracle.forward_f64(xr, idx, Wr), RTOL, ATOL, "bf16 y vs oracle on rounded inputs")
+    assert_close(gw, oracle.grad_w_f64(xr, idx, g), RTOL, ATOL, "bf16 grad_W vs oracle on rounded inputs")
+    assert_close(gx, oracle.grad_x_f64(idx, Wr, g, N), RTOL, gx_atol(L, K, N), "bf16 grad_x vs oracle on rounded inputs")
+    for got, ref, what in ((y, oracle.forward_f64(x, idx, W), "y"), (gw, oracle.grad_w_f64(x, idx, g), "grad_W"),
+                           (gx, oracle.grad_x_f64(idx, W, g, N), "grad_x")):
+        scale = np.abs(ref).max()
+        assert np.abs(got - ref).max() <= 2e-2 * scale, f"bf16 {what} further than 2e-2 from the fp32-input result"
+    with pytest.raises(TypeError):
+        ops._forward(xin, to_cuda(idx, dev), to_cuda(W, dev), None, transposed)  # mixed storage types
