@@ -302,7 +302,7 @@ bool narrow_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, Narro
 // complete inside the block and are added in a fixed order.  Rows of g start at arbitrary 4-byte
 // offsets (L is odd in practice), so a 256-byte row segment costs one extra 32-byte sector.
 constexpr int kTrO = 64;   // outputs per block
-__global__ void __launch_bounds__(256) transpose_g_kernel(const float* __restrict__ g, float* __restrict__ gT,
+__global__ void __launch_bounds__(256, 4) transpose_g_kernel(const float* __restrict__ g, float* __restrict__ gT,
                                                           float* __restrict__ gbias, int B, long long L,
                                                           long long ldg) {
     __shared__ float tile[128][kTrO + 1];
@@ -313,10 +313,11 @@ __global__ void __launch_bounds__(256) transpose_g_kernel(const float* __restric
     const bool ocol = o0 + tx < L;
     float colsum = 0.f;
     for (long long bb = 0; bb < ldg; bb += 128) {
-#pragma unroll
+        const float* src = g + static_cast<size_t>(bb + ty) * L + o0 + tx;
+#pragma unroll 16
         for (int u = 0; u < 32; ++u) {
             const long long b = bb + ty + 4 * u;
-            const float v = (ocol && b < B) ? __ldg(g + static_cast<size_t>(b) * L + o0 + tx) : 0.f;
+            const float v = (ocol && b < B) ? __ldcs(src + static_cast<size_t>(4 * u) * L) : 0.f;
             tile[ty + 4 * u][tx] = v;
             colsum += v;
         }
