@@ -23,6 +23,9 @@ STATUS_NAMES = {
 }
 FFI_F32 = 0
 FFI_BF16 = 1
+FFI_LOSS_BCE = 0
+FFI_LOSS_SQUARED_HINGE = 1
+FFI_LOSS_HINGE = 2
 
 # Every symbol include/ffi_b200.h declares.
 EXPORTED_SYMBOLS = (
@@ -32,7 +35,7 @@ EXPORTED_SYMBOLS = (
     "ffi_backward_workspace_bytes", "ffi_backward",
     "ffi_grad_x_static_max_scratch_bytes", "ffi_grad_x_static",
     "ffi_transposed_gradient_stride", "ffi_transpose_gradient",
-    "ffi_backward_from_transposed", "ffi_forward_bce_workspace_bytes", "ffi_forward_bce",
+    "ffi_backward_from_transposed", "ffi_forward_bce_workspace_bytes", "ffi_forward_bce", "ffi_forward_loss",
     "ffi_bce_workspace_bytes", "ffi_bce_grad", "ffi_adam_step",
 )
 
@@ -86,6 +89,8 @@ def _declare(lib):
     lib.ffi_forward_bce_workspace_bytes.argtypes = [i64, i64, i64, i64, i32, i32]
     lib.ffi_forward_bce.restype = i32
     lib.ffi_forward_bce.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, vp, sz, vp]
+    lib.ffi_forward_loss.restype = i32
+    lib.ffi_forward_loss.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, vp, sz, vp]
     lib.ffi_bce_workspace_bytes.restype = sz
     lib.ffi_bce_workspace_bytes.argtypes = [i64, i64]
     lib.ffi_bce_grad.restype = i32

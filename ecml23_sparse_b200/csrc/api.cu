@@ -383,11 +383,11 @@ extern "C" int ffi_backward_from_transposed(const void* x, const int32_t* idx, c
 
 namespace ffi {
 int launch_forward_bce_stream(const FwdArgs& a, float* gT, int64_t ldg, float scale, double* loss_partials, int* ctas,
-                              cudaStream_t stream, bool* handled);
+                              int loss_kind, cudaStream_t stream, bool* handled);
 int launch_bce_positive_fix(const float* xT, int64_t ldx, const int* idx, const float* W, const float* bias,
                             const int* row_ptr, const int* labels, float* gT, int64_t ldg, float* loss,
                             const double* partials, int nPartials, double* pos_partials, float scale, int B,
-                            int64_t L, int K, int64_t label_offset, cudaStream_t stream);
+                            int64_t L, int K, int64_t label_offset, int loss_kind, cudaStream_t stream);
 constexpr size_t kBcePartialBytes = 1024 * sizeof(double);  // >= one partial per CTA of the forward kernel
 }  // namespace ffi
 
@@ -397,21 +397,23 @@ extern "C" size_t ffi_forward_bce_workspace_bytes(int64_t B, int64_t N, int64_t 
            static_cast<size_t>(B > 0 ? B : 0) * sizeof(double);
 }
 
-extern "C" int ffi_forward_bce(const void* x, const int32_t* idx, const void* W, const float* bias,
-                               const int32_t* row_ptr, const int32_t* labels, float* gT, float* loss, int64_t B,
-                               int64_t N, int64_t L, int64_t K, int64_t L_total, int64_t label_offset, int x_transposed,
-                               int dtype, void* workspace, size_t workspace_bytes, void* stream_v) {
+extern "C" int ffi_forward_loss(int loss_kind, const void* x, const int32_t* idx, const void* W, const float* bias,
+                                const int32_t* row_ptr, const int32_t* labels, float* gT, float* loss, int64_t B,
+                                int64_t N, int64_t L, int64_t K, int64_t L_total, int64_t label_offset,
+                                int x_transposed, int dtype, void* workspace, size_t workspace_bytes, void* stream_v) {
     if (!x || !idx || !W || !row_ptr || !labels || !gT)
-        return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_forward_bce");
+        return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_forward_loss");
+    if (loss_kind != FFI_LOSS_BCE && loss_kind != FFI_LOSS_SQUARED_HINGE && loss_kind != FFI_LOSS_HINGE)
+        return fail(FFI_ERR_UNSUPPORTED, "unknown loss kind %d", loss_kind);
     int rc = check_shape(B, N, L, K);
     if (rc != FFI_OK) return rc;
-    if (dtype != FFI_F32) return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_bce: dtype %d not supported", dtype);
+    if (dtype != FFI_F32) return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_loss: dtype %d not supported", dtype);
     if (L_total < L) return fail(FFI_ERR_INVALID_ARGUMENT, "L_total must be >= L");
     if (reinterpret_cast<uintptr_t>(gT) % 16 != 0) return fail(FFI_ERR_INVALID_ARGUMENT, "gT must be 16-byte aligned");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     if (!workspace || reinterpret_cast<uintptr_t>(workspace) % kAlign != 0 ||
         workspace_bytes < ffi_forward_bce_workspace_bytes(B, N, L, K, x_transposed, dtype))
-        return fail(FFI_ERR_WORKSPACE, "ffi_forward_bce needs %zu bytes of %zu-byte aligned workspace",
+        return fail(FFI_ERR_WORKSPACE, "ffi_forward_loss needs %zu bytes of %zu-byte aligned workspace",
                     ffi_forward_bce_workspace_bytes(B, N, L, K, x_transposed, dtype), kAlign);
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     double* partials = reinterpret_cast<double*>(ws);
@@ -438,13 +440,22 @@ extern "C" int ffi_forward_bce(const void* x, const int32_t* idx, const void* W,
     const int64_t ldg = transposed_g_stride(B);
     int ctas = 0;
     bool handled = false;
-    rc = launch_forward_bce_stream(a, gT, ldg, scale, partials, &ctas, stream, &handled);
+    rc = launch_forward_bce_stream(a, gT, ldg, scale, partials, &ctas, loss_kind, stream, &handled);
     if (rc != FFI_OK) return rc;
     if (!handled)
-        return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_bce covers K %% 4 == 0 with x resident in shared memory; "
+        return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_loss covers K %% 4 == 0 with x resident in shared memory; "
                                          "use ffi_forward + ffi_bce_grad for this shape");
     if (static_cast<size_t>(ctas) * sizeof(double) > kBcePartialBytes)
         return fail(FFI_ERR_UNSUPPORTED, "too many loss partials (%d)", ctas);
     return launch_bce_positive_fix(xT, xp.ld, idx, a.W, bias, row_ptr, labels, gT, ldg, loss, partials, ctas,
-                                   pos_partials, scale, static_cast<int>(B), L, static_cast<int>(K), label_offset, stream);
+                                   pos_partials, scale, static_cast<int>(B), L, static_cast<int>(K), label_offset, loss_kind,
+                                   stream);
+}
+
+extern "C" int ffi_forward_bce(const void* x, const int32_t* idx, const void* W, const float* bias,
+                               const int32_t* row_ptr, const int32_t* labels, float* gT, float* loss, int64_t B,
+                               int64_t N, int64_t L, int64_t K, int64_t L_total, int64_t label_offset, int x_transposed,
+                               int dtype, void* workspace, size_t workspace_bytes, void* stream_v) {
+    return ffi_forward_loss(FFI_LOSS_BCE, x, idx, W, bias, row_ptr, labels, gT, loss, B, N, L, K, L_total, label_offset,
+                            x_transposed, dtype, workspace, workspace_bytes, stream_v);
 }

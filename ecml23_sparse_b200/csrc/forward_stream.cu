@@ -31,10 +31,20 @@ struct FwdStreamParams {
     long long ldg;
     float scale;
     double* loss_partials;
+    int loss_kind;  // ffi_loss_kind: BCE, squared hinge or hinge (for target 0; positives are corrected afterwards)
 };
 
-__device__ __forceinline__ float softplus_dev(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
-__device__ __forceinline__ float sigmoid_dev(float z) { return 1.f / (1.f + expf(-z)); }
+// loss and d(loss)/dz of one logit whose target is 0
+__device__ __forceinline__ void loss_negative(int kind, float z, float& value, float& grad) {
+    if (kind == 0) {
+        value = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
+        grad = 1.f / (1.f + expf(-z));
+    } else {
+        const float h = fmaxf(1.f + z, 0.f);
+        value = kind == 1 ? h * h : h;
+        grad = kind == 1 ? 2.f * h : (h > 0.f ? 1.f : 0.f);
+    }
+}
 
 template <int BPL, bool BCE>
 __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_stream_kernel(FwdStreamParams p) {
@@ -155,10 +165,13 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_stream_kernel(FwdStreamPa
                         const int b = b0 + lane + 32 * j;
                         const bool live = b < p.B;
                         const float zA = accA[j] + biasA, zB = accB[j] + biasB;
-                        if (live) loss_local += softplus_dev(zA) + (validB ? softplus_dev(zB) : 0.f);
+                        float vA, gA, vB, gB;
+                        loss_negative(p.loss_kind, zA, vA, gA);
+                        loss_negative(p.loss_kind, zB, vB, gB);
+                        if (live) loss_local += vA + (validB ? vB : 0.f);
                         if (b < p.ldg) {
-                            p.gT[static_cast<size_t>(oA) * p.ldg + b] = live ? p.scale * sigmoid_dev(zA) : 0.f;
-                            if (validB) p.gT[static_cast<size_t>(oA + 1) * p.ldg + b] = live ? p.scale * sigmoid_dev(zB) : 0.f;
+                            p.gT[static_cast<size_t>(oA) * p.ldg + b] = live ? p.scale * gA : 0.f;
+                            if (validB) p.gT[static_cast<size_t>(oA + 1) * p.ldg + b] = live ? p.scale * gB : 0.f;
                         }
                     }
                 } else {
@@ -231,6 +244,7 @@ struct BceEpilogue {
     float scale;
     double* loss_partials;
     int* ctas;  // out: number of CTAs = number of loss partials written
+    int loss_kind;
 };
 
 static int launch_forward_stream_impl(const FwdArgs& a, const BceEpilogue* bce, cudaStream_t stream, bool* handled) {
@@ -263,6 +277,7 @@ static int launch_forward_stream_impl(const FwdArgs& a, const BceEpilogue* bce, 
     p.ldg = bce ? bce->ldg : 0;
     p.scale = bce ? bce->scale : 0.f;
     p.loss_partials = bce ? bce->loss_partials : nullptr;
+    p.loss_kind = bce ? bce->loss_kind : 0;
     const int nBT = static_cast<int>(ceil_div(a.B, 32 * bpl));
     *handled = true;
     if (bce) {
@@ -284,8 +299,8 @@ int launch_forward_stream(const FwdArgs& a, cudaStream_t stream, bool* handled) 
 // padded batch columns) and one partial of sum softplus(z) per CTA; *ctas receives their number
 // (at most 2 * SM count).  *handled is false when the shape needs the unfused path.
 int launch_forward_bce_stream(const FwdArgs& a, float* gT, int64_t ldg, float scale, double* loss_partials, int* ctas,
-                              cudaStream_t stream, bool* handled) {
-    BceEpilogue e{gT, ldg, scale, loss_partials, ctas};
+                              int loss_kind, cudaStream_t stream, bool* handled) {
+    BceEpilogue e{gT, ldg, scale, loss_partials, ctas, loss_kind};
     return launch_forward_stream_impl(a, &e, stream, handled);
 }
 

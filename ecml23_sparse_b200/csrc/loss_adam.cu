@@ -103,14 +103,15 @@ __global__ void bce_finalize_kernel(const int* __restrict__ row_ptr, const int* 
     }
 }
 
-// After the forward kernel with the fused BCE epilogue: corrects gT at the positives
-// (g[b,o] = scale * (sigmoid(z) - 1) there), recomputing z of the few positive (b,o) pairs.
-// One block per sample; pos_partials[b] = sum of z over the sample's positives (fixed order).
+// After the forward kernel with the fused loss epilogue, which took every target as 0: corrects gT at
+// the positives (BCE: scale * (sigmoid(z) - 1); squared hinge: -2 * scale * max(0, 1 - z); hinge: -scale
+// where z < 1), recomputing z of the few positive (b,o) pairs.  One block per sample; pos_partials[b] = the sample's sum of
+// loss(z, target 1) - loss(z, target 0) over its positives (fixed order).
 __global__ void __launch_bounds__(256) bce_positive_fix_kernel(
     const float* __restrict__ xT, long long ldx, const int* __restrict__ idx, const float* __restrict__ W,
     const float* __restrict__ bias, const int* __restrict__ row_ptr, const int* __restrict__ labels,
     float* __restrict__ gT, long long ldg, double* __restrict__ pos_partials, float scale, long long L, int K,
-    long long label_offset) {
+    long long label_offset, int loss_kind) {
     __shared__ double sh[32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int b = blockIdx.x;
@@ -128,8 +129,20 @@ __global__ void __launch_bounds__(256) bce_positive_fix_kernel(
         for (int off = 16; off >= 1; off /= 2) z += __shfl_xor_sync(0xffffffffu, z, off);
         if (lane == 0) {
             z += bias ? bias[o] : 0.f;
-            possum += static_cast<double>(z);
-            gT[static_cast<size_t>(o) * ldg + b] -= scale;
+            // possum collects loss(target 1) - loss(target 0) of this logit
+            if (loss_kind == 0) {
+                possum -= static_cast<double>(z);
+                gT[static_cast<size_t>(o) * ldg + b] -= scale;
+            } else {
+                const float hp = fmaxf(1.f - z, 0.f), hn = fmaxf(1.f + z, 0.f);
+                if (loss_kind == 1) {
+                    possum += static_cast<double>(hp * hp) - static_cast<double>(hn * hn);
+                    gT[static_cast<size_t>(o) * ldg + b] = -2.f * hp * scale;
+                } else {
+                    possum += static_cast<double>(hp) - static_cast<double>(hn);
+                    gT[static_cast<size_t>(o) * ldg + b] = hp > 0.f ? -scale : 0.f;
+                }
+            }
         }
     }
     if (lane == 0) sh[warp] = possum;
@@ -141,14 +154,14 @@ __global__ void __launch_bounds__(256) bce_positive_fix_kernel(
     }
 }
 
-// loss = scale * (sum of the forward kernel's CTA partials of softplus(z) - sum of z over the positives).
+// loss = scale * (sum of the forward kernel's CTA partials (all targets taken as 0) + the positives' corrections).
 __global__ void __launch_bounds__(256) bce_loss_finalize_kernel(const double* __restrict__ partials, int nPartials,
                                                                 const double* __restrict__ pos_partials, int B,
                                                                 float scale, float* __restrict__ loss) {
     __shared__ double sh[32];
     double s = 0.0;
     for (int j = threadIdx.x; j < nPartials; j += blockDim.x) s += partials[j];
-    for (int j = threadIdx.x; j < B; j += blockDim.x) s -= pos_partials[j];
+    for (int j = threadIdx.x; j < B; j += blockDim.x) s += pos_partials[j];
     const double t = block_sum(s, sh);
     if (threadIdx.x == 0) *loss = static_cast<float>(t * static_cast<double>(scale));
 }
@@ -237,9 +250,9 @@ int launch_widen_bf16(const void* src, float* dst, int64_t n, cudaStream_t strea
 int launch_bce_positive_fix(const float* xT, int64_t ldx, const int* idx, const float* W, const float* bias,
                             const int* row_ptr, const int* labels, float* gT, int64_t ldg, float* loss,
                             const double* partials, int nPartials, double* pos_partials, float scale, int B,
-                            int64_t L, int K, int64_t label_offset, cudaStream_t stream) {
-    bce_positive_fix_kernel<<<static_cast<unsigned>(B), 256, 0, stream>>>(xT, ldx, idx, W, bias, row_ptr, labels, gT,
-                                                                          ldg, pos_partials, scale, L, K, label_offset);
+                            int64_t L, int K, int64_t label_offset, int loss_kind, cudaStream_t stream) {
+    bce_positive_fix_kernel<<<static_cast<unsigned>(B), 256, 0, stream>>>(
+        xT, ldx, idx, W, bias, row_ptr, labels, gT, ldg, pos_partials, scale, L, K, label_offset, loss_kind);
     if (loss) bce_loss_finalize_kernel<<<1, 256, 0, stream>>>(partials, nPartials, pos_partials, B, scale, loss);
     FFI_LAUNCH_CHECK("bce_positive_fix_kernel");
     return FFI_OK;

@@ -224,8 +224,10 @@ def _backward(features, lookup, weights, out_grad, transposed: bool, plan: Optio
 
 
 def forward_bce(features, lookup, weights, bias, row_ptr, labels, transposed: bool, total_labels=None,
-                label_offset: int = 0):
-    """Forward with the fused sigmoid-BCE gradient: returns (loss scalar tensor, gT[L][ldg]).
+                label_offset: int = 0, loss: str = "bce"):
+    """Forward with the loss gradient fused into its epilogue: returns (loss scalar tensor, gT[L][ldg]).
+    `loss` is "bce" (SparseBinaryCrossEntropyLoss), "squared_hinge" (SparseSquaredHingeLoss, the
+    one the reference's task files select) or "hinge" (SparseHingeLoss); sparse/metrics.py:132-173.
 
     The logits are never materialised.  Raises FFIError (FFI_ERR_UNSUPPORTED) for shapes the fused
     kernel does not cover; use `_forward` + `sparse_bce_with_logits` there."""
@@ -241,17 +243,19 @@ def forward_bce(features, lookup, weights, bias, row_ptr, labels, transposed: bo
         raise ValueError("row_ptr must have B+1 entries")
     ldg = int(lib.ffi_transposed_gradient_stride(B))
     gT = torch.empty((L, ldg), dtype=torch.float32, device=dev)
-    loss = torch.empty((), dtype=torch.float32, device=dev)
+    loss_out = torch.empty((), dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
         ws_bytes = lib.ffi_forward_bce_workspace_bytes(B, N, L, K, int(transposed), _lib.FFI_F32)
         ws = _workspace(dev, ws_bytes + 256)
         off = (-ws.data_ptr()) % 256
-        _lib.check(lib.ffi_forward_bce(features.data_ptr(), lookup.data_ptr(), weights.data_ptr(),
-                                       bias.data_ptr() if bias is not None else None, row_ptr.data_ptr(),
-                                       labels.data_ptr() if labels.numel() else row_ptr.data_ptr(), gT.data_ptr(),
-                                       loss.data_ptr(), B, N, L, K, total_labels or L, label_offset, int(transposed),
-                                       _lib.FFI_F32, ws.data_ptr() + off, ws.numel() - off, _stream_ptr(dev)))
-    return loss, gT
+        kind = {"bce": _lib.FFI_LOSS_BCE, "squared_hinge": _lib.FFI_LOSS_SQUARED_HINGE, "hinge": _lib.FFI_LOSS_HINGE}[loss]
+        _lib.check(lib.ffi_forward_loss(kind, features.data_ptr(), lookup.data_ptr(), weights.data_ptr(),
+                                        bias.data_ptr() if bias is not None else None, row_ptr.data_ptr(),
+                                        labels.data_ptr() if labels.numel() else row_ptr.data_ptr(), gT.data_ptr(),
+                                        loss_out.data_ptr(), B, N, L, K, total_labels or L, label_offset,
+                                        int(transposed), _lib.FFI_F32, ws.data_ptr() + off, ws.numel() - off,
+                                        _stream_ptr(dev)))
+    return loss_out, gT
 
 
 def transpose_gradient(out_grad: torch.Tensor, want_bias_grad: bool = False):

@@ -166,6 +166,22 @@ int ffi_forward_bce(const void* x, const int32_t* idx, const void* W, const floa
                     int x_transposed, int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The same fused forward + loss-gradient pass for each sparse loss of the reference
+ * (sparse/metrics.py:132-173): FFI_LOSS_BCE (as ffi_forward_bce), FFI_LOSS_SQUARED_HINGE (the
+ * "squared_hinge" its task files select, SparseSquaredHingeLoss, metrics.py:157-164) and
+ * FFI_LOSS_HINGE (SparseHingeLoss, metrics.py:146-154).  With m = (2t-1)*z and h = max(0, 1-m):
+ *   squared hinge: loss = mean h^2,  gT[o][b] = -2*(2t-1)*h / (B*L_total)
+ *   hinge:         loss = mean h,    gT[o][b] = -(2t-1)*[h > 0] / (B*L_total)
+ * The exact zeros of these gradients are what the reference's backward kernels skip
+ * (tfsparse/cc/kernels/backward.cu.h:73,94,131,151).
+ */
+typedef enum ffi_loss_kind { FFI_LOSS_BCE = 0, FFI_LOSS_SQUARED_HINGE = 1, FFI_LOSS_HINGE = 2 } ffi_loss_kind;
+int ffi_forward_loss(int loss_kind, const void* x, const int32_t* idx, const void* W, const float* bias,
+                     const int32_t* row_ptr, const int32_t* labels, float* gT, float* loss, int64_t B,
+                     int64_t N, int64_t L, int64_t K, int64_t L_total, int64_t label_offset,
+                     int x_transposed, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * grad_x without any allocation and without a caller workspace.  This entry point has no
  * counterpart in the reference.
  *

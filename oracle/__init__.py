@@ -66,6 +66,8 @@ def lib():
         L.oracle_transpose_index.restype = _int
         L.oracle_bce_f64.argtypes = [_F, _I, _I, _D, _i64, _i64]
         L.oracle_bce_f64.restype = ctypes.c_double
+        L.oracle_hinge_f64.argtypes = [_F, _I, _I, _D, _i64, _i64, ctypes.c_int]
+        L.oracle_hinge_f64.restype = ctypes.c_double
         L.oracle_adam_f64.argtypes = [_D, _D, _D, _D, _i64, ctypes.c_double, ctypes.c_double,
                                       ctypes.c_double, ctypes.c_double, _i64]
         _lib = L
@@ -221,6 +223,18 @@ def bce_f64(z, row_ptr, labels, want_grad=True):
     labels = _i32(labels)
     g = np.empty((B, L), np.float64) if want_grad else None
     loss = lib().oracle_bce_f64(_ptr(z, _F), _ptr(row_ptr, _I), _ptr(labels, _I), _ptr(g, _D), B, L)
+    return float(loss), g
+
+
+def hinge_f64(z, row_ptr, labels, squared=True, want_grad=True):
+    """(loss, g[B,L]) of the sparse hinge / squared hinge loss (sparse/metrics.py:146-164)."""
+    z = _f32(z)
+    B, L = z.shape
+    row_ptr = _i32(row_ptr)
+    labels = _i32(labels)
+    g = np.empty((B, L), np.float64) if want_grad else None
+    loss = lib().oracle_hinge_f64(_ptr(z, _F), _ptr(row_ptr, _I), _ptr(labels, _I), _ptr(g, _D), B, L,
+                                  int(bool(squared)))
     return float(loss), g
 
 

@@ -219,6 +219,40 @@ double oracle_bce_f64(const float* z, const int32_t* row_ptr, const int32_t* lab
     return total * scale;
 }
 
+/* Hinge (squared = 0) and squared hinge (squared = 1) losses with sparse multi-hot targets, fp64.
+ * Follows SparseHingeLoss / SparseSquaredHingeLoss (sparse/metrics.py:146-164) evaluated the way
+ * SparseLossBase.call does (sparse/metrics.py:136-139: every element with target 0, then the
+ * positives overwritten, sparse/utils.py:15-21), with the Keras batch mean:
+ * margin = (2t-1)*z, h = max(0, 1 - margin), element = h or h^2, mean over L then over B.
+ * Gradient g[b,o] = -(2t-1) * (h > 0 ? 1 : 0) / (B*L) (hinge; relu'(0) = 0 as in TensorFlow) or
+ * -(2t-1) * 2h / (B*L) (squared). */
+double oracle_hinge_f64(const float* z, const int32_t* row_ptr, const int32_t* labels, double* g,
+                        int64_t B, int64_t L, int squared) {
+    double scale = 1.0 / ((double)B * (double)L);
+    double total = 0.0;
+    for (int64_t b = 0; b < B; ++b) {
+        const float* zb = z + (size_t)b * (size_t)L;
+        double* gb = g ? g + (size_t)b * (size_t)L : NULL;
+        double row = 0.0;
+        for (int64_t o = 0; o < L; ++o) {
+            double h = 1.0 + (double)zb[o];
+            if (h < 0) h = 0;
+            row += squared ? h * h : h;
+            if (gb) gb[o] = squared ? 2.0 * h * scale : (h > 0 ? scale : 0.0);
+        }
+        for (int32_t e = row_ptr[b]; e < row_ptr[b + 1]; ++e) {
+            int32_t o = labels[e];
+            double hn = 1.0 + (double)zb[o], hp = 1.0 - (double)zb[o];
+            if (hn < 0) hn = 0;
+            if (hp < 0) hp = 0;
+            row += squared ? hp * hp - hn * hn : hp - hn;
+            if (gb) gb[o] = squared ? -2.0 * hp * scale : (hp > 0 ? -scale : 0.0);
+        }
+        total += row;
+    }
+    return total * scale;
+}
+
 /* One Adam step as Keras' Adam.update_step does (the optimizer sparse/optimizer.py:9-12
  * derives from): t = step (1-based), alpha = lr*sqrt(1-b2^t)/(1-b1^t),
  * m += (g-m)(1-b1), v += (g*g-v)(1-b2), w -= alpha*m/(sqrt(v)+eps).  fp64 state. */

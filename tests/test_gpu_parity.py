@@ -374,6 +374,45 @@ def test_fused_forward_bce_matches_unfused(cuda_device, shape, transposed):
     assert_close(gT_s[:, :B].t().cpu().numpy(), g_ref[:, lo:hi], 5e-5, 1e-12, "fused BCE gradient (shard)")
 
 
+@pytest.mark.parametrize("loss_name", ["squared_hinge", "hinge"])
+@pytest.mark.parametrize("shape,transposed", [((128, 768, 20_011, 32), True), ((37, 254, 513, 16), False)],
+                         ids=["headline-like", "small"])
+def test_fused_forward_hinge_losses(cuda_device, shape, transposed, loss_name):
+    """The reference's default loss (squared hinge) and the plain hinge, fused into the forward pass."""
+    dev = cuda_device
+    from ecml23_sparse_b200 import ops
+    B, N, L, K = shape
+    x, idx, W, _ = config_style_inputs(B, N, L, K, seed=11)
+    W = W * 8  # spread the logits over both sides of the hinge
+    bias = synth.normal(11, 40, (L,), std=0.5).numpy()
+    row_ptr, labels = synth.multi_hot_targets(11, 41, B, L)
+    xin = np.ascontiguousarray(x.T) if transposed else x
+    loss, gT = ops.forward_bce(to_cuda(xin, dev), to_cuda(idx, dev), to_cuda(W, dev), to_cuda(bias, dev), row_ptr,
+                               labels, transposed, loss=loss_name)
+    z64 = oracle.forward_f64(x, idx, W, bias=bias)
+    z = z64.astype(np.float32)
+    squared = loss_name == "squared_hinge"
+    loss_ref, g_ref = oracle.hinge_f64(z, row_ptr.numpy(), labels.numpy(), squared=squared)
+    assert abs(float(loss) - loss_ref) <= 2e-5 * abs(loss_ref) + 1e-7
+    got = gT[:, :B].t().cpu().numpy()
+    scale = 1.0 / (B * L)
+    assert (g_ref != 0).mean() > 0.05 and (g_ref == 0).mean() > 0.05, "test inputs must exercise both branches"
+    if squared:
+        # continuous in z: an fp32 logit within 1e-5 of the fp64 one moves the gradient by 2e-5 * scale
+        assert np.abs(got - g_ref).max() <= 4e-5 * scale * max(1.0, np.abs(z).max())
+    else:
+        # a step function of z: compare away from the kink at |z| = 1
+        away = np.abs(np.abs(z64) - 1.0) > 1e-4
+        assert away.mean() > 0.99
+        assert np.array_equal(got[away], g_ref[away].astype(np.float32))
+    assert not gT[:, B:].any()
+    lo, hi = L // 4, L // 4 + (L // 2) // 4 * 4
+    loss_s, gT_s = ops.forward_bce(to_cuda(xin, dev), to_cuda(idx[lo:hi], dev), to_cuda(W[lo:hi], dev),
+                                   to_cuda(bias[lo:hi], dev), row_ptr, labels, transposed, total_labels=L,
+                                   label_offset=lo, loss=loss_name)
+    assert torch.equal(gT_s[:, :B], gT[lo:hi, :B])
+
+
 def test_fused_forward_bce_reports_unsupported_shapes(cuda_device):
     dev = cuda_device
     from ecml23_sparse_b200 import ops

@@ -148,6 +148,38 @@ def test_bce_matches_closed_form():
     assert_close(g, (1 / (1 + np.exp(-zd)) - t) / (B * L), atol=1e-15, rtol=1e-12)
 
 
+@pytest.mark.parametrize("squared", [True, False])
+def test_hinge_losses_match_closed_form(squared):
+    rng = np.random.default_rng(3)
+    B, L = 6, 41
+    z = (rng.standard_normal((B, L)) * 2).astype(np.float32)
+    rows = [np.sort(rng.choice(L, size=rng.integers(0, 5), replace=False)) for _ in range(B)]
+    row_ptr = np.concatenate([[0], np.cumsum([len(r) for r in rows])]).astype(np.int32)
+    labels = np.concatenate(rows).astype(np.int32)
+    t = np.zeros((B, L))
+    for b, r in enumerate(rows):
+        t[b, r] = 1
+    zd = z.astype(np.float64)
+    sign = 2 * t - 1
+    h = np.maximum(1 - sign * zd, 0)
+    elem = h * h if squared else h
+    grad = (-sign * 2 * h if squared else -sign * (h > 0)) / (B * L)
+    loss, g = oracle.hinge_f64(z, row_ptr, labels, squared=squared)
+    assert abs(loss - elem.mean(axis=1).mean()) < 1e-12
+    assert_close(g, grad, atol=1e-15, rtol=1e-12)
+    # finite differences of the loss in a few coordinates away from the kink
+    eps = 1e-3
+    for (b, o) in [(0, 0), (2, 17), (5, 40)] + [(b, int(r[0])) for b, r in enumerate(rows) if len(r)][:2]:
+        if abs(h[b, o]) < 10 * eps:
+            continue
+        zp, zm = z.copy(), z.copy()
+        zp[b, o] += eps
+        zm[b, o] -= eps
+        fd = (oracle.hinge_f64(zp, row_ptr, labels, squared, False)[0]
+              - oracle.hinge_f64(zm, row_ptr, labels, squared, False)[0]) / (float(zp[b, o]) - float(zm[b, o]))
+        assert abs(fd - g[b, o]) < 1e-6 * max(1.0, abs(g[b, o]) * B * L) / (B * L) + 1e-9
+
+
 def test_adam_matches_textbook_form():
     rng = np.random.default_rng(1)
     n = 50
