@@ -22,6 +22,8 @@
 //     16 entries two lanes per entry add the buffer rows (fixed order) and store grad_W[o,k].
 // grad_x partials are flushed every few chunks and added in fp64 in a fixed order.
 // No atomics on floating-point data: results are bit-reproducible.
+#include <cuda.h>
+
 #include "ffi_common.cuh"
 
 namespace ffi {
@@ -353,6 +355,412 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_bwd_fused_kernel(BwdFusedPara
     }
 }
 
+// =====================================================================================
+// Batch 65..128: two entries per warp step, accumulators and x parked in tensor memory.
+//
+// A half warp covers the 128 batch columns of one entry (lane q of a half holds columns 4q..4q+3
+// and 64+4q..64+4q+3: two LDS.128, conflict-free without any swizzle), so the two halves of a
+// warp work on two consecutive entries of the same run at once.  Against one entry per warp step
+// this halves the entry fetches, the address arithmetic, the stores of the per-lane grad_W dots
+// and the rows the lane reduction reads.  Both halves accumulate grad_x of the same input; they
+// are added when a partial is flushed.
+//
+// A lane then needs 8 accumulators and 8 values of x[:, i] per input, too many registers for 8
+// inputs per warp.  Both live in tensor memory (TMEM, otherwise unused here): TMEM lane = thread
+// lane of the warp's quarter, 16 columns per input (8 sums | 8 x).  A run starts with one
+// tcgen05.ld of the 16 columns and ends with one tcgen05.st of the sums, so the loop over the
+// warp's inputs needs no unrolling and few registers.
+// =====================================================================================
+constexpr int kTmemCols = 512;            // per lane quarter: 4 warps x 8 inputs x 16 columns
+constexpr unsigned kPadCode = 0xffffffffu;  // code of the missing second entry of an odd run's last step
+
+__device__ __forceinline__ void tmem_alloc(void* smem_dst, unsigned ncols) {
+    const unsigned a = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(a), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_fence_before_sync() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_fence_after_sync() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// 8 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_store8(unsigned taddr, const unsigned (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+                 "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_wait_store() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_load8(unsigned taddr, unsigned (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+// Completes the loads; naming the registers keeps their first use behind the wait.
+__device__ __forceinline__ void tmem_wait_load(unsigned (&r)[8], unsigned (&s)[8]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(s[0]), "+r"(s[1]), "+r"(s[2]), "+r"(s[3]), "+r"(s[4]), "+r"(s[5]), "+r"(s[6]), "+r"(s[7])
+                 :
+                 : "memory");
+}
+
+// ---- mbarrier + TMA (one tiled bulk copy per g tile, no multicast) ------------------------------
+__device__ int g_wait_timeouts = 0;  // bounded waits that gave up (read by ffi_wait_timeouts)
+
+__device__ __forceinline__ unsigned smem_u32(const void* ptr) {
+    return static_cast<unsigned>(__cvta_generic_to_shared(ptr));
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+// Orders this thread's earlier generic-proxy accesses to shared memory before later async-proxy ones.
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Box of the 2-D tensor `map` with first element (x, y) -> dst; completion is signalled on `bar`.
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Waits for the phase with the given parity, at most about two seconds; false if it gave up.
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    while (!mbar_try_wait(bar, parity))
+        if (clock64() - start > 4000000000ll) return false;
+    return true;
+}
+
+// The 8 batch elements one lane of a half warp holds of a vector over the batch.
+struct Lane8 {
+    u64 a, b, c, d;
+    __device__ __forceinline__ void zero() { a = b = c = d = 0ull; }
+    __device__ __forceinline__ void set(const unsigned (&r)[8]) {
+        asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "r"(r[0]), "r"(r[1]));
+        asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "r"(r[2]), "r"(r[3]));
+        asm("mov.b64 %0, {%1, %2};" : "=l"(c) : "r"(r[4]), "r"(r[5]));
+        asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(r[6]), "r"(r[7]));
+    }
+    __device__ __forceinline__ void get(unsigned (&r)[8]) const {
+        asm("mov.b64 {%0, %1}, %2;" : "=r"(r[0]), "=r"(r[1]) : "l"(a));
+        asm("mov.b64 {%0, %1}, %2;" : "=r"(r[2]), "=r"(r[3]) : "l"(b));
+        asm("mov.b64 {%0, %1}, %2;" : "=r"(r[4]), "=r"(r[5]) : "l"(c));
+        asm("mov.b64 {%0, %1}, %2;" : "=r"(r[6]), "=r"(r[7]) : "l"(d));
+    }
+    // columns 4q..4q+3 at ptr, columns 64+4q..64+4q+3 256 bytes further
+    __device__ __forceinline__ void load_shared(const unsigned char* ptr) {
+        const ulonglong2 t0 = *reinterpret_cast<const ulonglong2*>(ptr);
+        const ulonglong2 t1 = *reinterpret_cast<const ulonglong2*>(ptr + 256);
+        a = t0.x, b = t0.y, c = t1.x, d = t1.y;
+    }
+    __device__ __forceinline__ void axpy(float w, const Lane8& g) {
+        const u64 ww = pack2(w, w);
+        a = fma2(ww, g.a, a), b = fma2(ww, g.b, b), c = fma2(ww, g.c, c), d = fma2(ww, g.d, d);
+    }
+    __device__ __forceinline__ float dot(const Lane8& g) const {
+        float lo, hi;
+        unpack2(fma2(g.d, d, fma2(g.c, c, fma2(g.b, b, mul2(g.a, a)))), lo, hi);
+        return lo + hi;
+    }
+};
+
+template <int NI>
+__global__ void __launch_bounds__(kThreads, 1)
+    ffi_bwd_pairs_kernel(BwdFusedParams p, const __grid_constant__ CUtensorMap g_map) {
+    constexpr int BT = 128;
+    constexpr int CPN = kWarps * NI + 1;
+    constexpr unsigned kRowMask = (1u << kKShift) - 1u;
+    static_assert(4 * NI * 16 <= kTmemCols, "the four warps of a lane quarter share the TMEM columns");
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+
+    const int T = p.T, K = p.K, L = p.L, N = p.N;
+    float* g_s = reinterpret_cast<float*>(smem_raw);                                    // [T][128], row-major
+    uint2* ent_s = reinterpret_cast<uint2*>(g_s + static_cast<size_t>(T) * BT);         // [2][entCap]
+    float* dbuf_s = reinterpret_cast<float*>(ent_s + 2 * p.entCap);                     // [warps][kSlots][kDRow]
+    int* cp_s = reinterpret_cast<int*>(dbuf_s + kWarps * kSlots * kDRow);               // [2][CPN]
+    unsigned long long* g_bar = reinterpret_cast<unsigned long long*>(cp_s + 2 * CPN);  // tile arrival (2*CPN ints keep 8-byte alignment)
+    unsigned* tmem_base_p = reinterpret_cast<unsigned*>(g_bar + 1);
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int half = lane >> 4;  // which entry of a pair this lane works on
+    const int q = lane & 15;
+    const int r = blockIdx.x;
+    const int i_lo = blockIdx.y * (kWarps * NI);
+    const int i_hi = min(N, i_lo + kWarps * NI);
+    const long long c_begin = p.nChunks * r / p.R;
+    const long long c_end = p.nChunks * (r + 1) / p.R;
+
+    if (warp == 0) tmem_alloc(tmem_base_p, kTmemCols);
+    if (tid == 32) mbar_init(g_bar, 1);
+    tmem_fence_before_sync();
+    __syncthreads();
+    tmem_fence_after_sync();
+    const unsigned tmem_base = *tmem_base_p;
+    // lanes 32*(warp % 4) .. +31 are the ones this warp may touch; its inputs take NI*16 columns
+    const unsigned taddr0 = tmem_base + ((static_cast<unsigned>(warp & 3) * 32u) << 16) +
+                            static_cast<unsigned>(warp >> 2) * (NI * 16);
+
+    for (int j = 0; j < NI; ++j) {
+        const int i = i_lo + warp * NI + j;
+        unsigned xv[8], zero[8];
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+            const int b = (m < 4 ? 0 : 64) + 4 * q + (m & 3);
+            xv[m] = __float_as_uint((i < N && b < p.B) ? __ldg(p.xT + static_cast<size_t>(i) * p.ldx + b) : 0.f);
+            zero[m] = 0u;
+        }
+        tmem_store8(taddr0 + j * 16, zero);
+        tmem_store8(taddr0 + j * 16 + 8, xv);
+    }
+    tmem_wait_store();
+
+    auto slice_bounds = [&](long long c, int& e_lo, int& cnt) {
+        const int* cptr_c = p.cptr + c * (N + 1);
+        e_lo = __ldg(cptr_c + i_lo);
+        cnt = __ldg(cptr_c + i_hi) - e_lo;
+    };
+
+    // Staging of a chunk's entries runs two chunks ahead of its walk: the flat positions (and the run
+    // offsets) are loaded into registers during the prologue two chunks earlier, and turned into
+    // entries (W by 4-byte cp.async, code = byte offset of the entry's g row | position in the chunk
+    // << 18) one chunk earlier, so that no prologue waits for a dependent global load.
+    // (The plan guarantees that a slice never holds more than entCap entries.)
+    int pos[kStageUnroll];
+    int cpv = 0;
+    auto load_pos = [&](long long c, int e_lo, int cnt) {
+        const int* cperm_c = p.cperm + c * static_cast<long long>(T) * K + e_lo;
+#pragma unroll
+        for (int u = 0; u < kStageUnroll; ++u) {
+            const int e = tid + u * kThreads;
+            pos[u] = e < cnt ? __ldg(cperm_c + e) : -1;
+        }
+        if (tid < CPN) cpv = __ldg(p.cptr + c * (N + 1) + min(i_lo + tid, i_hi)) - e_lo;
+    };
+    auto emit_one = [&](uint2* d, int ps, int pos0) {
+        __pipeline_memcpy_async(&d->x, p.W + ps, 4);
+        const int rel = ps - pos0;
+        const int ol = p.kShift >= 0 ? (rel >> p.kShift) : rel / K;
+        d->y = static_cast<unsigned>(ol * (BT * 4)) | (static_cast<unsigned>(rel) << kKShift);
+    };
+    auto emit = [&](long long c, int buf, int e_lo, int cnt) {
+        const int pos0 = static_cast<int>(c * T) * K;
+        uint2* dst = ent_s + buf * p.entCap;
+        if (tid < CPN) cp_s[buf * CPN + tid] = cpv;
+#pragma unroll
+        for (int u = 0; u < kStageUnroll; ++u)
+            if (pos[u] >= 0) emit_one(dst + tid + u * kThreads, pos[u], pos0);
+        // a slice with more entries than the registers cover: the rest is fetched here
+        const int* cperm_c = p.cperm + c * static_cast<long long>(T) * K + e_lo;
+        for (int e = tid + kStageUnroll * kThreads; e < cnt; e += kThreads) emit_one(dst + e, __ldg(cperm_c + e), pos0);
+    };
+
+    int pl_lo = 0, pl_cnt = 0;  // bounds of the chunk whose positions the registers hold
+    int nb_lo = 0, nb_cnt = 0;  // bounds of the chunk after that
+    if (c_begin < c_end) {
+        slice_bounds(c_begin, pl_lo, pl_cnt);
+        load_pos(c_begin, pl_lo, pl_cnt);
+        emit(c_begin, 0, pl_lo, pl_cnt);
+        if (c_begin + 1 < c_end) {
+            slice_bounds(c_begin + 1, pl_lo, pl_cnt);
+            load_pos(c_begin + 1, pl_lo, pl_cnt);
+        }
+        if (c_begin + 2 < c_end) slice_bounds(c_begin + 2, nb_lo, nb_cnt);
+    }
+    __pipeline_commit();
+    __pipeline_wait_prior(0);
+    float* dbuf = dbuf_s + warp * (kSlots * kDRow);
+    float* dlane = dbuf + lane;                                   // this lane's column of the dot buffer
+    unsigned* dcode = reinterpret_cast<unsigned*>(dbuf) + 32 + half;  // where lane q == 0 leaves its entry's code
+    const float4* drow = reinterpret_cast<const float4*>(dbuf + (lane >> 1) * kDRow + (lane & 1) * 16);
+    const unsigned* dmine = reinterpret_cast<const unsigned*>(dbuf) + (lane >> 1) * kDRow + 32 + (lane & 1);
+    const unsigned char* gs_lane = reinterpret_cast<const unsigned char*>(g_s) + q * 16;
+    bool gave_up = false;
+
+    long long c = c_begin;
+    for (; c < c_end; ++c) {
+        const int buf = static_cast<int>(c - c_begin) & 1;
+        const long long o0 = c * T;
+        // previous chunk's walk is done; buffer `buf` is staged; nobody has given up on a wait
+        if (__syncthreads_or(gave_up)) {
+            gave_up = true;
+            break;
+        }
+
+        // The g tile of the chunk: one TMA box [T rows][128 columns] of gT (rows past L arrive as zeros).
+        if (tid == 0) {
+            fence_proxy_async();
+            mbar_expect_tx(g_bar, static_cast<unsigned>(T) * (BT * 4));
+            tma_load_2d(g_s, &g_map, 0, static_cast<int>(o0), g_bar);
+        }
+        if (c + 1 < c_end) emit(c + 1, buf ^ 1, pl_lo, pl_cnt);
+        __pipeline_commit();
+        if (c + 2 < c_end) {
+            pl_lo = nb_lo, pl_cnt = nb_cnt;
+            load_pos(c + 2, pl_lo, pl_cnt);
+        }
+        if (c + 3 < c_end) slice_bounds(c + 3, nb_lo, nb_cnt);
+        // Each thread waits for the tile itself; one that gives up says so at the next barrier (the
+        // walk of this chunk then reads a stale tile, which is harmless: the result is void anyway).
+        if (!mbar_wait_bounded(g_bar, static_cast<unsigned>(c - c_begin) & 1u)) {
+            atomicAdd(&g_wait_timeouts, 1);
+            gave_up = true;
+        }
+
+        // ---- walk the runs of this warp's inputs, two entries per step ------------------------
+        const uint2* ent = ent_s + buf * p.entCap + half;  // this half's entry of a step
+        const int* cp = cp_s + buf * CPN + warp * NI;
+        float* gWc = p.gW ? p.gW + static_cast<size_t>(o0) * K : nullptr;
+        int slot = 0;  // steps buffered in the dot buffer (row = step, columns = lanes | 2 codes)
+
+        // Lane 2*row + h adds the 16 dots of half h of buffered step `row` (fixed order) and stores
+        // grad_W of that entry.
+        auto reduce_slots = [&]() {
+            __syncwarp();
+            const float4 q0 = drow[0], q1 = drow[1], q2 = drow[2], q3 = drow[3];
+            const unsigned code = *dmine;
+            const float sum = (((q0.x + q0.y) + (q0.z + q0.w)) + ((q1.x + q1.y) + (q1.z + q1.w))) +
+                              (((q2.x + q2.y) + (q2.z + q2.w)) + ((q3.x + q3.y) + (q3.z + q3.w)));
+            if ((lane >> 1) < slot && code != kPadCode && gWc) gWc[code >> kKShift] = sum;
+            __syncwarp();
+            slot = 0;
+        };
+
+#pragma unroll 1
+        for (int j = 0; j < NI; ++j) {
+            const int t = cp[j + 1];
+            int e = cp[j];
+            if (e >= t) continue;
+            Lane8 acc, xr;
+            {
+                unsigned av[8], xv[8];
+                tmem_load8(taddr0 + j * 16, av);
+                tmem_load8(taddr0 + j * 16 + 8, xv);
+                tmem_wait_load(av, xv);
+                acc.set(av);
+                xr.set(xv);
+            }
+            // two steps (four entries) per iteration: all loads are issued before the stores
+            for (; e + 4 <= t; e += 4) {
+                const uint2 en0 = ent[e], en1 = ent[e + 2];
+                Lane8 g0, g1;
+                g0.load_shared(gs_lane + (en0.y & kRowMask));
+                g1.load_shared(gs_lane + (en1.y & kRowMask));
+                if (slot + 2 > kSlots) reduce_slots();
+                acc.axpy(__uint_as_float(en0.x), g0);
+                acc.axpy(__uint_as_float(en1.x), g1);
+                dlane[slot * kDRow] = xr.dot(g0);
+                dlane[(slot + 1) * kDRow] = xr.dot(g1);
+                if (q == 0) {
+                    dcode[slot * kDRow] = en0.y;
+                    dcode[(slot + 1) * kDRow] = en1.y;
+                }
+                slot += 2;
+            }
+            if (e + 2 <= t) {
+                const uint2 en0 = ent[e];
+                Lane8 g0;
+                g0.load_shared(gs_lane + (en0.y & kRowMask));
+                if (slot == kSlots) reduce_slots();
+                acc.axpy(__uint_as_float(en0.x), g0);
+                dlane[slot * kDRow] = xr.dot(g0);
+                if (q == 0) dcode[slot * kDRow] = en0.y;
+                ++slot;
+                e += 2;
+            }
+            if (e < t) {  // odd run: the last step has an entry for half 0 only
+                uint2 en0 = make_uint2(0u, kPadCode);
+                Lane8 g0;
+                g0.zero();
+                if (half == 0) {
+                    en0 = ent[e];
+                    g0.load_shared(gs_lane + (en0.y & kRowMask));
+                }
+                if (slot == kSlots) reduce_slots();
+                acc.axpy(__uint_as_float(en0.x), g0);
+                dlane[slot * kDRow] = xr.dot(g0);
+                if (q == 0) dcode[slot * kDRow] = en0.y;
+                ++slot;
+            }
+            {
+                unsigned av[8];
+                acc.get(av);
+                tmem_store8(taddr0 + j * 16, av);
+            }
+        }
+        if (slot > 0) reduce_slots();
+        tmem_wait_store();
+
+        __pipeline_wait_prior(0);  // this thread's staged weights of the next chunk are in place
+
+        // Every segChunks chunks the running grad_x sums go out as one partial and restart from zero.
+        const long long done = c - c_begin + 1;
+        if (done % p.segChunks == 0 || c + 1 == c_end) {
+            const int seg = static_cast<int>((done - 1) / p.segChunks);
+            for (int j = 0; j < NI; ++j) {
+                const int i = i_lo + warp * NI + j;
+                unsigned av[8], zero[8];
+                tmem_load8(taddr0 + j * 16, av);
+#pragma unroll
+                for (int m = 0; m < 8; ++m) zero[m] = 0u;
+                tmem_wait_load(av, zero);
+                tmem_store8(taddr0 + j * 16, zero);
+                float out[8];
+#pragma unroll
+                for (int m = 0; m < 8; ++m) {
+                    out[m] = __uint_as_float(av[m]);
+                    out[m] += __shfl_xor_sync(0xffffffffu, out[m], 16);  // the two halves
+                }
+                if (i < N && half == 0) {
+                    float* dst = p.partial + ((static_cast<size_t>(r) * p.S + seg) * N + i) * p.Bpad + 4 * q;
+                    *reinterpret_cast<float4*>(dst) = make_float4(out[0], out[1], out[2], out[3]);
+                    *reinterpret_cast<float4*>(dst + 64) = make_float4(out[4], out[5], out[6], out[7]);
+                }
+            }
+            tmem_wait_store();
+        }
+    }
+
+    // Segments a range never reached hold zeros (ranges differ by at most one chunk).
+    for (int seg = static_cast<int>((c_end - c_begin + p.segChunks - 1) / p.segChunks); seg < p.S; ++seg) {
+        for (int j = 0; j < NI; ++j) {
+            const int i = i_lo + warp * NI + j;
+            if (i < N && half == 0) {
+                float* dst = p.partial + ((static_cast<size_t>(r) * p.S + seg) * N + i) * p.Bpad + 4 * q;
+                *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4*>(dst + 64) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+    }
+
+    // A CTA that gave up waits once more, again bounded, for the copy it abandoned before it leaves.
+    if (gave_up && c < c_end) mbar_wait_bounded(g_bar, static_cast<unsigned>(c - c_begin) & 1u);
+    tmem_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+}
+
 struct FusedConfig {
     int bpl, ni, iparts, Bpad, R, entCap, segChunks, S;
     size_t smem;
@@ -387,6 +795,32 @@ bool fused_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, FusedC
     c->entCap = static_cast<int>(cap);
     c->smem = total;
     return true;
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link libcuda).
+int encode_g_map(CUtensorMap* map, const float* gT, int64_t L, int64_t ldg, int chunk_rows) {
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        FFI_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+        if (q != cudaDriverEntryPointSuccess || !fn) return fail(FFI_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    if (reinterpret_cast<uintptr_t>(gT) % 16 != 0 || chunk_rows > 256)
+        return fail(FFI_ERR_INVALID_ARGUMENT, "transposed gradient must be 16-byte aligned, chunks at most 256 rows");
+    const cuuint64_t dims[2] = {128, static_cast<cuuint64_t>(L)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldg) * 4};
+    const cuuint32_t box[2] = {128, static_cast<cuuint32_t>(chunk_rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(gT), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(FFI_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", static_cast<int>(r));
+    return FFI_OK;
 }
 
 template <int NI, int BPL>
@@ -455,7 +889,22 @@ int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, floa
     p.entCap = c.entCap;
     p.segChunks = c.segChunks;
     p.S = c.S;
-    if (c.bpl == 4) rc = launch_fused_t<8, 4>(p, c, stream);
+    // the pair kernel's entry code holds the position within the chunk in 14 bits
+    const bool pairs = c.bpl == 4 && static_cast<long long>(a.plan->chunk_rows) * a.K <= (1 << (32 - kKShift));
+    if (c.bpl == 4 && !pairs) rc = launch_fused_t<8, 4>(p, c, stream);
+    else if (c.bpl == 4) {
+        // gT as a 2-D tensor [L rows][128 columns] with row pitch ldg; one box = the g tile of a chunk
+        CUtensorMap g_map;
+        rc = encode_g_map(&g_map, a.gT, a.L, a.ldg, a.plan->chunk_rows);
+        if (rc != FFI_OK) return rc;
+        auto kern = ffi_bwd_pairs_kernel<8>;
+        const size_t smem = c.smem + 1024;  // barrier and TMEM slot behind the arrays, alignment slack
+        FFI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        dim3 grid(static_cast<unsigned>(c.R), static_cast<unsigned>(c.iparts), 1);
+        kern<<<grid, kThreads, smem, stream>>>(p, g_map);
+        FFI_LAUNCH_CHECK("ffi_bwd_pairs_kernel");
+        rc = FFI_OK;
+    }
     else if (c.bpl == 2) rc = launch_fused_t<16, 2>(p, c, stream);
     else rc = launch_fused_t<32, 1>(p, c, stream);
     if (rc != FFI_OK) return rc;
@@ -463,3 +912,11 @@ int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, floa
 }
 
 }  // namespace ffi
+
+// Number of bounded device-side waits that gave up since the library was loaded (0 in a healthy
+// run; any other value means the results of the affected call are void).  Synchronises the device.
+extern "C" int ffi_wait_timeouts(int* out) {
+    if (!out) return ffi::fail(FFI_ERR_INVALID_ARGUMENT, "NULL output passed to ffi_wait_timeouts");
+    FFI_CUDA_CHECK(cudaMemcpyFromSymbol(out, ffi::g_wait_timeouts, sizeof(int)));
+    return FFI_OK;
+}

@@ -215,6 +215,14 @@ int ffi_grad_x_static(const float* W, const float* gT, int64_t ldg, const ffi_pl
                       float* grad_x, int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed,
                       void* stream);
 
+/*
+ * The fused backward waits for its bulk copies with a time limit (about two seconds) instead of
+ * forever; a wait that runs out is counted and the kernel winds down.  *out receives the count since
+ * the library was loaded: 0 in a healthy process, anything else voids the calls that ran since the
+ * last check.  Synchronises the device.  No counterpart in the reference.
+ */
+int ffi_wait_timeouts(int* out);
+
 /* ------------------------------------------------------------ loss / Adam ---- */
 
 /*

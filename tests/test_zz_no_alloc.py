@@ -77,3 +77,23 @@ def test_static_scratch_rejects_oversize_and_bad_arguments(cuda_device):
                                  None) == 1
     assert lib.ffi_grad_x_static(W.data_ptr(), gT.data_ptr(), 4096, plan.handle, out.data_ptr(), B, N, L + 1, K, 0,
                                  None) == 5
+
+
+def test_no_device_wait_gave_up(cuda_device):
+    """Collected last: after every backward call of the session, no bounded device-side wait (the
+    bulk copies of the fused backward) may have run out."""
+    import ctypes
+
+    # one more fused backward at a batch that takes the bulk-copy path
+    B, N, L, K = 128, 256, 4099, 32
+    dev = cuda_device
+    x = torch.randn(B, N, device=dev)
+    idx = torch.stack([torch.randperm(N, device=dev)[:K] for _ in range(L)]).to(torch.int32)
+    W = torch.randn(L, K, device=dev) * 0.1
+    g = torch.randn(B, L, device=dev)
+    gx, gw, _ = _backward(x, idx, W, g, False)
+    ref_gw = torch.einsum("bl,blk->lk", g, x[:, idx.long()])
+    assert torch.allclose(gw, ref_gw, rtol=1e-4, atol=1e-4)
+    count = ctypes.c_int(-1)
+    _lib.check(_lib.load().ffi_wait_timeouts(ctypes.byref(count)))
+    assert count.value == 0
