@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_bwd_fused_kernel(BwdFusedPara
     constexpr int CPN = kWarps * NI + 1;
     constexpr unsigned kRowMask = (1u << kKShift) - 1u;
     using LV = LaneVec<BPL>;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
 
     const int T = p.T, K = p.K, L = p.L, N = p.N;
     float* g_s = reinterpret_cast<float*>(smem_raw);                                    // [T][BT] swizzled
@@ -455,18 +455,6 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsig
 struct Lane8 {
     u64 a, b, c, d;
     __device__ __forceinline__ void zero() { a = b = c = d = 0ull; }
-    __device__ __forceinline__ void set(const unsigned (&r)[8]) {
-        asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "r"(r[0]), "r"(r[1]));
-        asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "r"(r[2]), "r"(r[3]));
-        asm("mov.b64 %0, {%1, %2};" : "=l"(c) : "r"(r[4]), "r"(r[5]));
-        asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(r[6]), "r"(r[7]));
-    }
-    __device__ __forceinline__ void get(unsigned (&r)[8]) const {
-        asm("mov.b64 {%0, %1}, %2;" : "=r"(r[0]), "=r"(r[1]) : "l"(a));
-        asm("mov.b64 {%0, %1}, %2;" : "=r"(r[2]), "=r"(r[3]) : "l"(b));
-        asm("mov.b64 {%0, %1}, %2;" : "=r"(r[4]), "=r"(r[5]) : "l"(c));
-        asm("mov.b64 {%0, %1}, %2;" : "=r"(r[6]), "=r"(r[7]) : "l"(d));
-    }
     // columns 4q..4q+3 at ptr, columns 64+4q..64+4q+3 256 bytes further
     __device__ __forceinline__ void load_shared(const unsigned char* ptr) {
         const ulonglong2 t0 = *reinterpret_cast<const ulonglong2*>(ptr);
@@ -484,16 +472,43 @@ struct Lane8 {
     }
 };
 
-template <int NI>
-__global__ void __launch_bounds__(kThreads, 1)
+// 16 columns of this thread's TMEM lane -> (sums, x) of one input, complete on return.  The 32-bit
+// halves are paired inside the asm block so that the loaded registers ARE the pairs.
+__device__ __forceinline__ void tmem_load_input(unsigned taddr, Lane8& sums, Lane8& x) {
+    asm volatile(
+        "{\n"
+        ".reg .b32 t<16>;\n"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15}, [%8];\n"
+        "tcgen05.wait::ld.sync.aligned;\n"
+        "mov.b64 %0, {t0, t1};\n mov.b64 %1, {t2, t3};\n mov.b64 %2, {t4, t5};\n mov.b64 %3, {t6, t7};\n"
+        "mov.b64 %4, {t8, t9};\n mov.b64 %5, {t10, t11};\n mov.b64 %6, {t12, t13};\n mov.b64 %7, {t14, t15};\n"
+        "}"
+        : "=l"(sums.a), "=l"(sums.b), "=l"(sums.c), "=l"(sums.d), "=l"(x.a), "=l"(x.b), "=l"(x.c), "=l"(x.d)
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_store_sums(unsigned taddr, const Lane8& sums) {
+    asm volatile(
+        "{\n"
+        ".reg .b32 t<8>;\n"
+        "mov.b64 {t0, t1}, %1;\n mov.b64 {t2, t3}, %2;\n mov.b64 {t4, t5}, %3;\n mov.b64 {t6, t7}, %4;\n"
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {t0, t1, t2, t3, t4, t5, t6, t7};\n"
+        "}" ::"r"(taddr),
+        "l"(sums.a), "l"(sums.b), "l"(sums.c), "l"(sums.d)
+        : "memory");
+}
+
+template <int NI, int THREADS, int SLOTS>
+__global__ void __launch_bounds__(THREADS, 1)
     ffi_bwd_pairs_kernel(BwdFusedParams p, const __grid_constant__ CUtensorMap g_map) {
     constexpr int BT = 128;
+    constexpr int kThreads = THREADS, kWarps = THREADS / 32, kSlots = SLOTS;  // shadow the file-wide values
     constexpr int CPN = kWarps * NI + 1;
     constexpr unsigned kRowMask = (1u << kKShift) - 1u;
-    static_assert(4 * NI * 16 <= kTmemCols, "the four warps of a lane quarter share the TMEM columns");
+    static_assert((THREADS / 128) * NI * 16 <= kTmemCols, "the warps of a lane quarter share the TMEM columns");
     extern __shared__ __align__(1024) unsigned char smem_raw[];
 
-    const int T = p.T, K = p.K, L = p.L, N = p.N;
+    const int T = p.T, K = p.K, N = p.N;
     float* g_s = reinterpret_cast<float*>(smem_raw);                                    // [T][128], row-major
     uint2* ent_s = reinterpret_cast<uint2*>(g_s + static_cast<size_t>(T) * BT);         // [2][entCap]
     float* dbuf_s = reinterpret_cast<float*>(ent_s + 2 * p.entCap);                     // [warps][kSlots][kDRow]
@@ -521,6 +536,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // lanes 32*(warp % 4) .. +31 are the ones this warp may touch; its inputs take NI*16 columns
     const unsigned taddr0 = tmem_base + ((static_cast<unsigned>(warp & 3) * 32u) << 16) +
                             static_cast<unsigned>(warp >> 2) * (NI * 16);
+    static_assert(SLOTS == 16 || SLOTS == 8, "the lane reduction maps lanes to (row, half)");
 
     for (int j = 0; j < NI; ++j) {
         const int i = i_lo + warp * NI + j;
@@ -592,10 +608,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     __pipeline_wait_prior(0);
     float* dbuf = dbuf_s + warp * (kSlots * kDRow);
     float* dlane = dbuf + lane;                                   // this lane's column of the dot buffer
-    unsigned* dcode = reinterpret_cast<unsigned*>(dbuf) + 32 + half;  // where lane q == 0 leaves its entry's code
-    const float4* drow = reinterpret_cast<const float4*>(dbuf + (lane >> 1) * kDRow + (lane & 1) * 16);
-    const unsigned* dmine = reinterpret_cast<const unsigned*>(dbuf) + (lane >> 1) * kDRow + 32 + (lane & 1);
+    const int dcode_delta = 32 + half - lane;                     // from a lane's dot to its entry's code
+    const float* dlast1 = dlane + (kSlots - 1) * kDRow;           // last row a single step may fill
+    const float* dlast2 = dlane + (kSlots - 2) * kDRow;           // last row a double step may start at
+    const int myrow = min(lane >> 1, kSlots - 1);  // lanes past 2*kSlots idle in the reduction
+    const float4* drow = reinterpret_cast<const float4*>(dbuf + myrow * kDRow + (lane & 1) * 16);
+    const unsigned* dmine = reinterpret_cast<const unsigned*>(dbuf) + myrow * kDRow + 32 + (lane & 1);
     const unsigned char* gs_lane = reinterpret_cast<const unsigned char*>(g_s) + q * 16;
+    const unsigned tileBytes = static_cast<unsigned>(T) * (BT * 4);
     bool gave_up = false;
 
     long long c = c_begin;
@@ -609,9 +629,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
 
         // The g tile of the chunk: one TMA box [T rows][128 columns] of gT (rows past L arrive as zeros).
+        // (A second tile buffer filled one chunk ahead was measured: it needs T <= 168 to fit, and the
+        // shorter runs cost more than the hidden copy saves.)
         if (tid == 0) {
             fence_proxy_async();
-            mbar_expect_tx(g_bar, static_cast<unsigned>(T) * (BT * 4));
+            mbar_expect_tx(g_bar, tileBytes);
             tma_load_2d(g_s, &g_map, 0, static_cast<int>(o0), g_bar);
         }
         if (c + 1 < c_end) emit(c + 1, buf ^ 1, pl_lo, pl_cnt);
@@ -632,61 +654,56 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint2* ent = ent_s + buf * p.entCap + half;  // this half's entry of a step
         const int* cp = cp_s + buf * CPN + warp * NI;
         float* gWc = p.gW ? p.gW + static_cast<size_t>(o0) * K : nullptr;
-        int slot = 0;  // steps buffered in the dot buffer (row = step, columns = lanes | 2 codes)
+        // Row of the dot buffer the next step fills: 32 per-lane dots, then the codes of its two entries.
+        // dptr points at this lane's column of that row; the code of the lane's entry goes to
+        // dptr + dcode_delta (written by every lane of the half: same address, same value).
+        float* dptr = dlane;
 
         // Lane 2*row + h adds the 16 dots of half h of buffered step `row` (fixed order) and stores
         // grad_W of that entry.
         auto reduce_slots = [&]() {
             __syncwarp();
+            const int rows = static_cast<int>(dptr - dlane) / kDRow;
             const float4 q0 = drow[0], q1 = drow[1], q2 = drow[2], q3 = drow[3];
             const unsigned code = *dmine;
             const float sum = (((q0.x + q0.y) + (q0.z + q0.w)) + ((q1.x + q1.y) + (q1.z + q1.w))) +
                               (((q2.x + q2.y) + (q2.z + q2.w)) + ((q3.x + q3.y) + (q3.z + q3.w)));
-            if ((lane >> 1) < slot && code != kPadCode && gWc) gWc[code >> kKShift] = sum;
+            if ((lane >> 1) < rows && lane < 2 * kSlots && code != kPadCode && gWc) gWc[code >> kKShift] = sum;
             __syncwarp();
-            slot = 0;
+            dptr = dlane;
         };
 
+        int e = cp[0];
 #pragma unroll 1
         for (int j = 0; j < NI; ++j) {
             const int t = cp[j + 1];
-            int e = cp[j];
             if (e >= t) continue;
             Lane8 acc, xr;
-            {
-                unsigned av[8], xv[8];
-                tmem_load8(taddr0 + j * 16, av);
-                tmem_load8(taddr0 + j * 16 + 8, xv);
-                tmem_wait_load(av, xv);
-                acc.set(av);
-                xr.set(xv);
-            }
+            tmem_load_input(taddr0 + j * 16, acc, xr);
             // two steps (four entries) per iteration: all loads are issued before the stores
             for (; e + 4 <= t; e += 4) {
                 const uint2 en0 = ent[e], en1 = ent[e + 2];
                 Lane8 g0, g1;
                 g0.load_shared(gs_lane + (en0.y & kRowMask));
                 g1.load_shared(gs_lane + (en1.y & kRowMask));
-                if (slot + 2 > kSlots) reduce_slots();
+                if (dptr > dlast2) reduce_slots();
                 acc.axpy(__uint_as_float(en0.x), g0);
                 acc.axpy(__uint_as_float(en1.x), g1);
-                dlane[slot * kDRow] = xr.dot(g0);
-                dlane[(slot + 1) * kDRow] = xr.dot(g1);
-                if (q == 0) {
-                    dcode[slot * kDRow] = en0.y;
-                    dcode[(slot + 1) * kDRow] = en1.y;
-                }
-                slot += 2;
+                dptr[0] = xr.dot(g0);
+                dptr[kDRow] = xr.dot(g1);
+                reinterpret_cast<unsigned*>(dptr + dcode_delta)[0] = en0.y;
+                reinterpret_cast<unsigned*>(dptr + dcode_delta)[kDRow] = en1.y;
+                dptr += 2 * kDRow;
             }
             if (e + 2 <= t) {
                 const uint2 en0 = ent[e];
                 Lane8 g0;
                 g0.load_shared(gs_lane + (en0.y & kRowMask));
-                if (slot == kSlots) reduce_slots();
+                if (dptr > dlast1) reduce_slots();
                 acc.axpy(__uint_as_float(en0.x), g0);
-                dlane[slot * kDRow] = xr.dot(g0);
-                if (q == 0) dcode[slot * kDRow] = en0.y;
-                ++slot;
+                dptr[0] = xr.dot(g0);
+                reinterpret_cast<unsigned*>(dptr + dcode_delta)[0] = en0.y;
+                dptr += kDRow;
                 e += 2;
             }
             if (e < t) {  // odd run: the last step has an entry for half 0 only
@@ -697,19 +714,16 @@ __global__ void __launch_bounds__(kThreads, 1)
                     en0 = ent[e];
                     g0.load_shared(gs_lane + (en0.y & kRowMask));
                 }
-                if (slot == kSlots) reduce_slots();
+                if (dptr > dlast1) reduce_slots();
                 acc.axpy(__uint_as_float(en0.x), g0);
-                dlane[slot * kDRow] = xr.dot(g0);
-                if (q == 0) dcode[slot * kDRow] = en0.y;
-                ++slot;
+                dptr[0] = xr.dot(g0);
+                reinterpret_cast<unsigned*>(dptr + dcode_delta)[0] = en0.y;
+                dptr += kDRow;
+                e = t;
             }
-            {
-                unsigned av[8];
-                acc.get(av);
-                tmem_store8(taddr0 + j * 16, av);
-            }
+            tmem_store_sums(taddr0 + j * 16, acc);
         }
-        if (slot > 0) reduce_slots();
+        if (dptr != dlane) reduce_slots();
         tmem_wait_store();
 
         __pipeline_wait_prior(0);  // this thread's staged weights of the next chunk are in place
@@ -897,11 +911,14 @@ int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, floa
         CUtensorMap g_map;
         rc = encode_g_map(&g_map, a.gT, a.L, a.ldg, a.plan->chunk_rows);
         if (rc != FFI_OK) return rc;
-        auto kern = ffi_bwd_pairs_kernel<8>;
-        const size_t smem = c.smem + 1024;  // barrier and TMEM slot behind the arrays, alignment slack
+        constexpr int PT = 512, PNI = 8, PSL = 16;  // (1024 threads x 4 inputs was measured: 10 % slower)
+        auto kern = ffi_bwd_pairs_kernel<PNI, PT, PSL>;
+        // as fused_config's total, with this variant's dot buffers; + barriers, TMEM slot, slack
+        const size_t smem = c.smem - static_cast<size_t>(kWarps) * kSlots * kDRow * 4 +
+                            static_cast<size_t>(PT / 32) * PSL * kDRow * 4 + 1024;
         FFI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         dim3 grid(static_cast<unsigned>(c.R), static_cast<unsigned>(c.iparts), 1);
-        kern<<<grid, kThreads, smem, stream>>>(p, g_map);
+        kern<<<grid, PT, smem, stream>>>(p, g_map);
         FFI_LAUNCH_CHECK("ffi_bwd_pairs_kernel");
         rc = FFI_OK;
     }
