@@ -372,7 +372,7 @@ def run_ours(args):
         "transpose_g": (8 * B * Ls + 4 * Ls, 0),
         "backward_fused": (4 * B * Ls + 8 * Ls * K + 4 * Ls * K + 8 * B * N, 2 * fma_pass),
     }
-    names = {"forward": "ffi_fwd_stream_kernel", "transpose_g": "transpose_g_kernel", "backward_fused": "ffi_bwd_pairs_kernel" if B > 64 else "ffi_bwd_fused_kernel"}
+    names = {"forward": "ffi_fwd_pair_kernel", "transpose_g": "transpose_g_kernel", "backward_fused": "ffi_bwd_pairs_kernel" if B > 64 else "ffi_bwd_fused_kernel"}
     kernels = {}
     for name, ms in kernel_ms.items():
         nbytes, fmas = work[name]

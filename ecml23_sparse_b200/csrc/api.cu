@@ -277,7 +277,7 @@ static int backward_impl(const void* x, const int32_t* idx, const void* W, const
             return fail(FFI_ERR_INVALID_ARGUMENT, "gT needs a row stride that is a multiple of 32 and >= B, 16-byte aligned");
         if (sep_w && !gw_stream)
             return fail(FFI_ERR_UNSUPPORTED, "this shape needs the untransposed gradient g[B,L] for grad_W");
-        if (grad_bias) {
+        if (grad_bias && !fused) {  // the fused backward sums grad_bias from the g tiles it loads
             rc = launch_bias_grad_rows(gT_in, ldg_in, L, grad_bias, stream);
             if (rc != FFI_OK) return rc;
             bias_done = true;
@@ -323,7 +323,7 @@ static int backward_impl(const void* x, const int32_t* idx, const void* W, const
         if (rc != FFI_OK) return rc;
         ax.workspace = part;
         ax.workspace_bytes = workspace_bytes - (static_cast<unsigned char*>(part) - ws);
-        return launch_backward_fused(ax, xT, ldx, grad_w, stream);
+        return launch_backward_fused(ax, xT, ldx, grad_w, bias_done ? nullptr : grad_bias, stream);
     }
 
     if (grad_w || (grad_bias && !bias_done)) {

@@ -123,6 +123,7 @@ struct BwdFusedParams {
     const int* cptr;
     float* partial;  // [R*S][N][Bpad]
     float* gW;
+    float* gbias;  // pair kernel only: grad_bias[o] = sum_b gT[o][b], from the g tiles it holds anyway
     int B, N, L, K;
     int kShift;  // log2(K) when K is a power of two, else -1
     int T;
@@ -470,6 +471,11 @@ struct Lane8 {
         unpack2(fma2(g.d, d, fma2(g.c, c, fma2(g.b, b, mul2(g.a, a)))), lo, hi);
         return lo + hi;
     }
+    __device__ __forceinline__ float sum() const {
+        float f[8];
+        unpack2(a, f[0], f[1]), unpack2(b, f[2], f[3]), unpack2(c, f[4], f[5]), unpack2(d, f[6], f[7]);
+        return ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
+    }
 };
 
 // 16 columns of this thread's TMEM lane -> (sums, x) of one input, complete on return.  The 32-bit
@@ -648,6 +654,18 @@ __global__ void __launch_bounds__(THREADS, 1)
         if (!mbar_wait_bounded(g_bar, static_cast<unsigned>(c - c_begin) & 1u)) {
             atomicAdd(&g_wait_timeouts, 1);
             gave_up = true;
+        }
+
+        // grad_bias of the chunk's rows: the slices of a range take turns, each row is a half warp's sum
+        if (p.gbias && static_cast<int>(c % gridDim.y) == static_cast<int>(blockIdx.y)) {
+            for (int rr = 2 * warp + half; rr < T; rr += 2 * kWarps) {
+                Lane8 v;
+                v.load_shared(gs_lane + rr * (BT * 4));
+                float sum = v.sum();
+#pragma unroll
+                for (int off = 8; off >= 1; off /= 2) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                if (q == 0 && o0 + rr < p.L) p.gbias[o0 + rr] = sum;
+            }
         }
 
         // ---- walk the runs of this warp's inputs, two entries per step ------------------------
@@ -867,8 +885,10 @@ size_t backward_fused_workspace_bytes(const ffi_plan* plan, int64_t B) {
 int reduce_range_partials(const float* partial, float* gx, int R, int N, int B, int Bpad, int x_transposed,
                           cudaStream_t stream);
 
-// grad_x (always) and grad_W (when gW != nullptr) in one kernel.  xT is x as [N][ldx].
-int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, float* gW, cudaStream_t stream) {
+// grad_x (always), grad_W (when gW != nullptr) and grad_bias (when gbias != nullptr, from gT) in one
+// kernel (grad_bias by a separate pass over gT where the pair kernel does not apply).  xT is x as [N][ldx].
+int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, float* gW, float* gbias,
+                          cudaStream_t stream) {
     DeviceInfo dev;
     int rc = get_device_info(&dev);
     if (rc != FFI_OK) return rc;
@@ -889,6 +909,7 @@ int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, floa
     p.cptr = a.plan->cptr;
     p.partial = static_cast<float*>(a.workspace);
     p.gW = gW;
+    p.gbias = nullptr;
     p.B = a.B;
     p.N = a.N;
     p.L = a.L;
@@ -905,6 +926,11 @@ int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, floa
     p.S = c.S;
     // the pair kernel's entry code holds the position within the chunk in 14 bits
     const bool pairs = c.bpl == 4 && static_cast<long long>(a.plan->chunk_rows) * a.K <= (1 << (32 - kKShift));
+    if (gbias && !pairs) {  // the other kernels leave grad_bias to a pass over gT
+        rc = launch_bias_grad_rows(a.gT, a.ldg, a.L, gbias, stream);
+        if (rc != FFI_OK) return rc;
+    }
+    if (pairs) p.gbias = gbias;
     if (c.bpl == 4 && !pairs) rc = launch_fused_t<8, 4>(p, c, stream);
     else if (c.bpl == 4) {
         // gT as a 2-D tensor [L rows][128 columns] with row pitch ldg; one box = the g tile of a chunk

@@ -147,6 +147,7 @@ int launch_grad_x(const GradXArgs& a, cudaStream_t stream);
 // grad_x and grad_W in one pass over the transposed index (narrow inputs, batch <= 128).
 bool backward_fused_applicable(const ffi_plan* plan, int64_t B);
 size_t backward_fused_workspace_bytes(const ffi_plan* plan, int64_t B);
-int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, float* gW, cudaStream_t stream);
+int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, float* gW, float* gbias,
+                          cudaStream_t stream);
 
 }  // namespace ffi

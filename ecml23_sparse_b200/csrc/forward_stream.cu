@@ -36,8 +36,12 @@ struct FwdStreamParams {
 // loss and d(loss)/dz of one logit whose target is 0
 __device__ __forceinline__ void loss_negative(int kind, float z, float& value, float& grad) {
     if (kind == 0) {
-        value = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
-        grad = 1.f / (1.f + expf(-z));
+        // one exponential serves both: s = exp(-|z|), softplus(z) = max(z,0) + log(1+s),
+        // sigmoid(z) = 1/(1+s) or s/(1+s); hardware approximations (a few ulp) are well inside 1e-5
+        const float s = __expf(-fabsf(z));
+        const float r = __fdividef(1.f, 1.f + s);
+        value = fmaxf(z, 0.f) + __logf(1.f + s);
+        grad = z >= 0.f ? r : s * r;
     } else {
         const float h = fmaxf(1.f + z, 0.f);
         value = kind == 1 ? h * h : h;
