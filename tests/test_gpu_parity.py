@@ -105,6 +105,8 @@ EXTRA_SHAPES = [
     (5, 7, 33, 1), (9, 10, 50, 3), (31, 129, 300, 32), (33, 130, 301, 33), (64, 64, 257, 64),
     (65, 255, 1000, 72), (128, 768, 2049, 32), (129, 100, 513, 5), (200, 37, 700, 12), (2, 2, 1, 2),
     (32, 768, 20_011, 32), (128, 768, 20_011, 32), (256, 512, 4_099, 32),
+    # batch 65..128 takes the half-warp backward: partial last slice, many slices, long and short runs
+    (100, 300, 5_000, 16), (96, 130, 777, 8), (128, 64, 4_000, 4), (127, 2_000, 3_000, 32), (66, 768, 511, 64),
 ]
 
 
