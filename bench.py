@@ -36,7 +36,7 @@ FMA_PER_CLK_PER_SM = 128
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch at the headline shape, from the ncu capture
 # summarised in profiles/dram_traffic_headline_B128_N768_L670091_K32.md (None for other shapes).
-NCU_TRAFFIC_BYTES = {"forward": 194.3e6 + 302.0e6, "transpose_g": 343.1e6 + 299.2e6, "backward_fused": 523.6e6 + 114.0e6}
+NCU_TRAFFIC_BYTES = {"forward": 195.1e6 + 302.4e6, "transpose_g": 345.8e6 + 283.2e6, "backward_fused": 523.4e6 + 113.5e6}
 
 
 def parse_args():
