@@ -36,6 +36,7 @@ EXPORTED_SYMBOLS = (
     "ffi_grad_x_static_max_scratch_bytes", "ffi_grad_x_static",
     "ffi_transposed_gradient_stride", "ffi_transpose_gradient",
     "ffi_backward_from_transposed", "ffi_forward_bce_workspace_bytes", "ffi_forward_bce", "ffi_forward_loss", "ffi_wait_timeouts",
+    "ffi_forward_topk_workspace_bytes", "ffi_forward_topk",
     "ffi_bce_workspace_bytes", "ffi_bce_grad", "ffi_adam_step",
 )
 
@@ -91,6 +92,10 @@ def _declare(lib):
     lib.ffi_forward_bce.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, vp, sz, vp]
     lib.ffi_forward_loss.restype = i32
     lib.ffi_forward_loss.argtypes = [i32, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, vp, sz, vp]
+    lib.ffi_forward_topk_workspace_bytes.restype = sz
+    lib.ffi_forward_topk_workspace_bytes.argtypes = [i64, i64, i64, i64, i32, i32]
+    lib.ffi_forward_topk.restype = i32
+    lib.ffi_forward_topk.argtypes = [vp, vp, vp, vp, vp, vp, i32, i64, i64, i64, i64, i64, i32, i32, vp, sz, vp]
     lib.ffi_wait_timeouts.restype = i32
     lib.ffi_wait_timeouts.argtypes = [vp]
     lib.ffi_bce_workspace_bytes.restype = sz

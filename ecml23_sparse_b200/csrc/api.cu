@@ -384,6 +384,9 @@ extern "C" int ffi_backward_from_transposed(const void* x, const int32_t* idx, c
 namespace ffi {
 int launch_forward_bce_stream(const FwdArgs& a, float* gT, int64_t ldg, float scale, double* loss_partials, int* ctas,
                               int loss_kind, cudaStream_t stream, bool* handled);
+size_t forward_topk_workspace_bytes(int64_t B);
+int launch_forward_topk_stream(const FwdArgs& a, void* scratch, float* top_val, int* top_idx, int kk, int label_offset,
+                               cudaStream_t stream, bool* handled);
 int launch_bce_positive_fix(const float* xT, int64_t ldx, const int* idx, const float* W, const float* bias,
                             const int* row_ptr, const int* labels, float* gT, int64_t ldg, float* loss,
                             const double* partials, int nPartials, double* pos_partials, float scale, int B,
@@ -450,6 +453,55 @@ extern "C" int ffi_forward_loss(int loss_kind, const void* x, const int32_t* idx
     return launch_bce_positive_fix(xT, xp.ld, idx, a.W, bias, row_ptr, labels, gT, ldg, loss, partials, ctas,
                                    pos_partials, scale, static_cast<int>(B), L, static_cast<int>(K), label_offset, loss_kind,
                                    stream);
+}
+
+extern "C" size_t ffi_forward_topk_workspace_bytes(int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed,
+                                                   int dtype) {
+    return ffi_forward_workspace_bytes(B, N, L, K, x_transposed, dtype) + kAlign + align_up(forward_topk_workspace_bytes(B));
+}
+
+extern "C" int ffi_forward_topk(const void* x, const int32_t* idx, const void* W, const float* bias, float* top_val,
+                                int32_t* top_idx, int k, int64_t B, int64_t N, int64_t L, int64_t K,
+                                int64_t label_offset, int x_transposed, int dtype, void* workspace,
+                                size_t workspace_bytes, void* stream_v) {
+    if (!x || !idx || !W || !top_val || !top_idx)
+        return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_forward_topk");
+    int rc = check_shape(B, N, L, K);
+    if (rc != FFI_OK) return rc;
+    if (dtype != FFI_F32) return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_topk: dtype %d not supported", dtype);
+    if (label_offset < 0 || label_offset + L >= (1LL << 31))
+        return fail(FFI_ERR_INVALID_ARGUMENT, "label_offset + L must fit 31 bits");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const size_t need = ffi_forward_topk_workspace_bytes(B, N, L, K, x_transposed, dtype);
+    if (!workspace || reinterpret_cast<uintptr_t>(workspace) % kAlign != 0 || workspace_bytes < need)
+        return fail(FFI_ERR_WORKSPACE, "ffi_forward_topk needs %zu bytes of %zu-byte aligned workspace", need, kAlign);
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    void* lists = ws;
+    float* xws = reinterpret_cast<float*>(ws + align_up(forward_topk_workspace_bytes(B)));
+
+    const bool smem = forward_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
+    const XPlan xp = plan_x(smem, B, N, x_transposed);
+    const float* xT = nullptr;
+    rc = stage_x(xp, static_cast<const float*>(x), xws, B, N, x_transposed, stream, &xT);
+    if (rc != FFI_OK) return rc;
+    FwdArgs a;
+    a.xT = xT;
+    a.ldx = xp.ld;
+    a.idx = idx;
+    a.W = static_cast<const float*>(W);
+    a.bias = bias;
+    a.y = nullptr;
+    a.B = static_cast<int>(B);
+    a.N = static_cast<int>(N);
+    a.L = static_cast<int>(L);
+    a.K = static_cast<int>(K);
+    bool handled = false;
+    rc = launch_forward_topk_stream(a, lists, top_val, top_idx, k, static_cast<int>(label_offset), stream, &handled);
+    if (rc != FFI_OK) return rc;
+    if (!handled)
+        return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_topk covers K %% 4 == 0 with x resident in shared memory; "
+                                         "use ffi_forward and a top-k over y for this shape");
+    return FFI_OK;
 }
 
 extern "C" int ffi_forward_bce(const void* x, const int32_t* idx, const void* W, const float* bias,

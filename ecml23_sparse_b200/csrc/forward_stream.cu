@@ -31,7 +31,30 @@ struct FwdStreamParams {
     float scale;
     double* loss_partials;
     int loss_kind;  // ffi_loss_kind: BCE, squared hinge or hinge (for target 0; positives are corrected afterwards)
+    // top-k epilogue: every warp keeps, per batch element of the tile, the kTopK best logits of the
+    // rows it computed; lists [tile][cta][warp][batch][kTopK] of (value, row) go to `topk_lists`
+    uint2* topk_lists;
 };
+
+constexpr int kTopK = 8;  // capacity of a top-k list (P@1, P@3, P@5 need 5)
+
+// Sorted (value descending, row ascending) insertion; `better` orders candidates the way
+// tf.nn.top_k does: higher value first, lower index on ties.
+__device__ __forceinline__ bool topk_better(float v, int i, float v2, int i2) { return v > v2 || (v == v2 && i < i2); }
+__device__ __forceinline__ void topk_insert(float (&tv)[kTopK], int (&ti)[kTopK], float v, int i) {
+    if (!topk_better(v, i, tv[kTopK - 1], ti[kTopK - 1])) return;
+    tv[kTopK - 1] = v;
+    ti[kTopK - 1] = i;
+#pragma unroll
+    for (int j = kTopK - 1; j >= 1; --j) {
+        if (topk_better(tv[j], ti[j], tv[j - 1], ti[j - 1])) {
+            const float fv = tv[j];
+            const int fi = ti[j];
+            tv[j] = tv[j - 1], ti[j] = ti[j - 1];
+            tv[j - 1] = fv, ti[j - 1] = fi;
+        }
+    }
+}
 
 // loss and d(loss)/dz of one logit whose target is 0
 __device__ __forceinline__ void loss_negative(int kind, float z, float& value, float& grad) {
@@ -61,8 +84,9 @@ __device__ __forceinline__ int pair_column(int q, int j) {
     else return VPL * q + j;
 }
 
-template <int VPL, bool BCE>
+template <int VPL, int MODE>
 __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_pair_kernel(FwdStreamParams p) {
+    constexpr bool BCE = MODE == 1;  // 0: write y; 1: loss epilogue; 2: running top-k of the logits
     constexpr int BT = 16 * VPL;
     constexpr int S = BT + 8;  // result-tile row stride: 16-byte rows, conflict-free for both access patterns
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -121,6 +145,14 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_pair_kernel(FwdStreamPara
     if (qd < numQuads) issue(2 * qd, 0);
     int s = 0;
     float loss_local = 0.f;
+    // top-k mode: lane keeps the lists of batch columns lane, lane + 32, ... of the tile
+    constexpr int TM = MODE == 2 ? (BT + 31) / 32 : 1;
+    float tv[TM][kTopK];
+    int ti[TM][kTopK];
+#pragma unroll
+    for (int m = 0; m < TM; ++m)
+#pragma unroll
+        for (int j = 0; j < kTopK; ++j) tv[m][j] = -INFINITY, ti[m][j] = 0x7fffffff;
     for (; qd < numQuads; qd += GW) {
 #pragma unroll
         for (int half = 0; half < 2; ++half, ++s) {
@@ -203,7 +235,20 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_pair_kernel(FwdStreamPara
             }
             __syncwarp();
         }
-        if constexpr (!BCE) {
+        if constexpr (MODE == 2) {
+            const long long oq = 4 * qd;
+#pragma unroll
+            for (int m = 0; m < TM; ++m) {
+                const int bl = lane + 32 * m;
+                if (bl < BT && b0 + bl < p.B) {
+#pragma unroll
+                    for (int oo = 0; oo < 4; ++oo)
+                        if (oq + oo < L) topk_insert(tv[m], ti[m], ys[oo * S + bl], static_cast<int>(oq + oo));
+                }
+            }
+            __syncwarp();
+        }
+        if constexpr (MODE == 0) {
             const long long oq = 4 * qd;
 #pragma unroll
             for (int it = 0; it < BT * 4 / 32; ++it) {
@@ -216,6 +261,19 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_pair_kernel(FwdStreamPara
         }
     }
     __pipeline_wait_prior(0);
+
+    if constexpr (MODE == 2) {
+        uint2* out = p.topk_lists +
+                     ((static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * kWarps + warp) * (BT * kTopK);
+#pragma unroll
+        for (int m = 0; m < TM; ++m) {
+            const int bl = lane + 32 * m;
+            if (bl < BT)
+#pragma unroll
+                for (int j = 0; j < kTopK; ++j)
+                    out[bl * kTopK + j] = make_uint2(__float_as_uint(tv[m][j]), static_cast<unsigned>(ti[m][j]));
+        }
+    }
 
     if constexpr (BCE) {
         double v = static_cast<double>(loss_local);
@@ -233,10 +291,10 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_pair_kernel(FwdStreamPara
     }
 }
 
-template <int VPL, bool BCE>
+template <int VPL, int MODE>
 int launch_pair_t(const FwdStreamParams& p, size_t smem, int nBT, const DeviceInfo& dev, cudaStream_t stream,
                   int* ctas_out) {
-    auto kern = ffi_fwd_pair_kernel<VPL, BCE>;
+    auto kern = ffi_fwd_pair_kernel<VPL, MODE>;
     FFI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     int occ = 0;
     FFI_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kThreads, smem));
@@ -252,6 +310,59 @@ int launch_pair_t(const FwdStreamParams& p, size_t smem, int nBT, const DeviceIn
     return FFI_OK;
 }
 
+// One block per batch element: the best kk of all warp lists of its tile, in tf.nn.top_k order.
+__global__ void __launch_bounds__(256) topk_merge_kernel(const uint2* __restrict__ lists, int listsPerTile, int BT,
+                                                         int B, int kk, int label_offset,
+                                                         float* __restrict__ out_val, int* __restrict__ out_idx) {
+    __shared__ float sv[256][kTopK];
+    __shared__ int si[256][kTopK];
+    const int b = blockIdx.x;
+    const int tile = b / BT, bl = b - tile * BT;
+    float tv[kTopK];
+    int ti[kTopK];
+#pragma unroll
+    for (int j = 0; j < kTopK; ++j) tv[j] = -INFINITY, ti[j] = 0x7fffffff;
+    for (int l = threadIdx.x; l < listsPerTile; l += blockDim.x) {
+        const uint2* src = lists + (static_cast<size_t>(tile) * listsPerTile + l) * (BT * kTopK) + bl * kTopK;
+#pragma unroll
+        for (int j = 0; j < kTopK; ++j) {
+            const uint2 c = src[j];
+            topk_insert(tv, ti, __uint_as_float(c.x), static_cast<int>(c.y));
+        }
+    }
+    // tree over the threads: 256 -> 32 -> 1 lists
+    for (int width = 256; width > 1; width /= 8) {
+#pragma unroll
+        for (int j = 0; j < kTopK; ++j) sv[threadIdx.x][j] = tv[j], si[threadIdx.x][j] = ti[j];
+        __syncthreads();
+        const int next = width / 8;
+        if (static_cast<int>(threadIdx.x) < next) {
+            for (int u = 1; u < 8; ++u) {
+                const int src = threadIdx.x + u * next;
+#pragma unroll
+                for (int j = 0; j < kTopK; ++j) topk_insert(tv, ti, sv[src][j], si[src][j]);
+            }
+        }
+        __syncthreads();
+        if (next < 8 && next > 1) {  // 4 lists left: thread 0 finishes
+#pragma unroll
+            for (int j = 0; j < kTopK; ++j) sv[threadIdx.x][j] = tv[j], si[threadIdx.x][j] = ti[j];
+            __syncthreads();
+            if (threadIdx.x == 0)
+                for (int u = 1; u < next; ++u)
+#pragma unroll
+                    for (int j = 0; j < kTopK; ++j) topk_insert(tv, ti, sv[u][j], si[u][j]);
+            break;
+        }
+    }
+    if (threadIdx.x == 0) {
+        for (int j = 0; j < kk; ++j) {
+            out_val[static_cast<size_t>(b) * kk + j] = tv[j];
+            out_idx[static_cast<size_t>(b) * kk + j] = ti[j] == 0x7fffffff ? -1 : ti[j] + label_offset;
+        }
+    }
+}
+
 }  // namespace
 
 // Shared launcher: BCE epilogue when bce != nullptr.
@@ -263,8 +374,14 @@ struct BceEpilogue {
     int* ctas;  // out: number of CTAs = number of loss partials written
     int loss_kind;
 };
+struct TopkEpilogue {
+    uint2* lists;  // scratch from forward_topk_workspace_bytes
+    int* ctas_x;   // out: CTAs per batch tile
+    int* bt;       // out: batch tile width
+};
 
-static int launch_forward_stream_impl(const FwdArgs& a, const BceEpilogue* bce, cudaStream_t stream, bool* handled) {
+static int launch_forward_stream_impl(const FwdArgs& a, const BceEpilogue* bce, const TopkEpilogue* topk,
+                                      cudaStream_t stream, bool* handled) {
     *handled = false;
     DeviceInfo dev;
     int rc = get_device_info(&dev);
@@ -295,22 +412,32 @@ static int launch_forward_stream_impl(const FwdArgs& a, const BceEpilogue* bce, 
     p.scale = bce ? bce->scale : 0.f;
     p.loss_partials = bce ? bce->loss_partials : nullptr;
     p.loss_kind = bce ? bce->loss_kind : 0;
+    p.topk_lists = topk ? topk->lists : nullptr;
     const int nBT = static_cast<int>(ceil_div(a.B, 32 * bpl));
     *handled = true;
     // same tile sizes and shared-memory footprint: BT = 32 * bpl = 16 * VPL
-    if (bce) {
-        if (bpl == 4) return launch_pair_t<8, true>(p, smem, nBT, dev, stream, bce->ctas);
-        if (bpl == 2) return launch_pair_t<4, true>(p, smem, nBT, dev, stream, bce->ctas);
-        return launch_pair_t<2, true>(p, smem, nBT, dev, stream, bce->ctas);
+    if (topk) {
+        int ctas = 0;
+        if (bpl == 4) rc = launch_pair_t<8, 2>(p, smem, nBT, dev, stream, &ctas);
+        else if (bpl == 2) rc = launch_pair_t<4, 2>(p, smem, nBT, dev, stream, &ctas);
+        else rc = launch_pair_t<2, 2>(p, smem, nBT, dev, stream, &ctas);
+        *topk->ctas_x = ctas / nBT;
+        *topk->bt = 32 * bpl;
+        return rc;
     }
-    if (bpl == 4) return launch_pair_t<8, false>(p, smem, nBT, dev, stream, nullptr);
-    if (bpl == 2) return launch_pair_t<4, false>(p, smem, nBT, dev, stream, nullptr);
-    return launch_pair_t<2, false>(p, smem, nBT, dev, stream, nullptr);
+    if (bce) {
+        if (bpl == 4) return launch_pair_t<8, 1>(p, smem, nBT, dev, stream, bce->ctas);
+        if (bpl == 2) return launch_pair_t<4, 1>(p, smem, nBT, dev, stream, bce->ctas);
+        return launch_pair_t<2, 1>(p, smem, nBT, dev, stream, bce->ctas);
+    }
+    if (bpl == 4) return launch_pair_t<8, 0>(p, smem, nBT, dev, stream, nullptr);
+    if (bpl == 2) return launch_pair_t<4, 0>(p, smem, nBT, dev, stream, nullptr);
+    return launch_pair_t<2, 0>(p, smem, nBT, dev, stream, nullptr);
 }
 
 // Launches the barrier-free kernel when the shape allows it; *handled tells the caller.
 int launch_forward_stream(const FwdArgs& a, cudaStream_t stream, bool* handled) {
-    return launch_forward_stream_impl(a, nullptr, stream, handled);
+    return launch_forward_stream_impl(a, nullptr, nullptr, stream, handled);
 }
 
 // Forward with the fused sigmoid-BCE epilogue: writes gT[o][b] = scale * sigmoid(z[b,o]) (zero in the
@@ -319,7 +446,31 @@ int launch_forward_stream(const FwdArgs& a, cudaStream_t stream, bool* handled) 
 int launch_forward_bce_stream(const FwdArgs& a, float* gT, int64_t ldg, float scale, double* loss_partials, int* ctas,
                               int loss_kind, cudaStream_t stream, bool* handled) {
     BceEpilogue e{gT, ldg, scale, loss_partials, ctas, loss_kind};
-    return launch_forward_stream_impl(a, &e, stream, handled);
+    return launch_forward_stream_impl(a, &e, nullptr, stream, handled);
+}
+
+// Scratch for the warp lists of forward_topk: an upper bound over the grids the launcher may choose.
+size_t forward_topk_workspace_bytes(int64_t B) {
+    DeviceInfo dev;
+    if (get_device_info(&dev) != FFI_OK) return 0;
+    // tiles * CTAs per tile <= SM count (one CTA per SM), BT <= 128
+    const size_t lists = static_cast<size_t>(dev.sm_count + ceil_div(B, 32)) * kWarps;
+    return lists * 128 * kTopK * sizeof(uint2);
+}
+
+// Forward whose epilogue keeps the best logits per batch element instead of writing y; top_val/top_idx
+// [B][kk] receive them in tf.nn.top_k order (row + label_offset as the index).  *handled as above.
+int launch_forward_topk_stream(const FwdArgs& a, void* scratch, float* top_val, int* top_idx, int kk, int label_offset,
+                               cudaStream_t stream, bool* handled) {
+    if (kk < 1 || kk > kTopK) return fail(FFI_ERR_UNSUPPORTED, "top-k supports 1 <= k <= %d", kTopK);
+    int ctas_x = 0, bt = 0;
+    TopkEpilogue e{static_cast<uint2*>(scratch), &ctas_x, &bt};
+    int rc = launch_forward_stream_impl(a, nullptr, &e, stream, handled);
+    if (rc != FFI_OK || !*handled) return rc;
+    topk_merge_kernel<<<static_cast<unsigned>(a.B), 256, 0, stream>>>(static_cast<const uint2*>(scratch), ctas_x * kWarps,
+                                                                      bt, a.B, kk, label_offset, top_val, top_idx);
+    FFI_LAUNCH_CHECK("topk_merge_kernel");
+    return FFI_OK;
 }
 
 }  // namespace ffi

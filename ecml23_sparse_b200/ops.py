@@ -258,6 +258,53 @@ def forward_bce(features, lookup, weights, bias, row_ptr, labels, transposed: bo
     return loss_out, gT
 
 
+def forward_topk(features, lookup, weights, bias, k: int, transposed: bool, label_offset: int = 0):
+    """The k highest logits per sample and their labels, (values[B,k], labels[B,k] int32), in the order
+    of tf.nn.top_k, without materialising the logits: what PrecisionAtK (sparse/metrics.py:9-70)
+    consumes.  With a sharded label dimension call it per shard (`label_offset` = first label of the
+    shard) and merge the candidates with `merge_topk`."""
+    features = _check_cuda("features", features, (torch.float32,))
+    weights = _check_cuda("weights", weights, (torch.float32,))
+    lookup = _as_index(lookup)
+    B, N, L, K = _shapes(features, lookup, weights, transposed)
+    dev = features.device
+    lib = _lib.load()
+    top_val = torch.empty((B, k), dtype=torch.float32, device=dev)
+    top_idx = torch.empty((B, k), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        ws_bytes = lib.ffi_forward_topk_workspace_bytes(B, N, L, K, int(transposed), _lib.FFI_F32)
+        ws = _workspace(dev, ws_bytes + 256)
+        off = (-ws.data_ptr()) % 256
+        _lib.check(lib.ffi_forward_topk(features.data_ptr(), lookup.data_ptr(), weights.data_ptr(),
+                                        bias.data_ptr() if bias is not None else None, top_val.data_ptr(),
+                                        top_idx.data_ptr(), k, B, N, L, K, label_offset, int(transposed),
+                                        _lib.FFI_F32, ws.data_ptr() + off, ws.numel() - off, _stream_ptr(dev)))
+    return top_val, top_idx
+
+
+def merge_topk(candidates, k: int):
+    """Best k of several shards' (values, labels) candidate lists, again in tf.nn.top_k order."""
+    vals = torch.cat([c[0] for c in candidates], dim=1)
+    idxs = torch.cat([c[1] for c in candidates], dim=1)
+    # value descending, label ascending on ties: sort by label first, then a stable sort by value
+    order = torch.argsort(idxs, dim=1, stable=True)
+    vals, idxs = torch.gather(vals, 1, order), torch.gather(idxs, 1, order)
+    order = torch.argsort(vals, dim=1, descending=True, stable=True)[:, :k]
+    return torch.gather(vals, 1, order), torch.gather(idxs, 1, order)
+
+
+def precision_at_k(top_labels: torch.Tensor, row_ptr: torch.Tensor, labels: torch.Tensor, k: int) -> float:
+    """P@k of a batch as PrecisionAtK accumulates it (sparse/metrics.py:58-70): the number of the k
+    top-ranked labels that are true labels, summed over the batch, divided by B*k."""
+    top = top_labels[:, :k].to(torch.int64).cpu()
+    row_ptr, labels = row_ptr.cpu().to(torch.int64), labels.cpu().to(torch.int64)
+    correct = 0
+    for b in range(top.shape[0]):
+        truth = labels[row_ptr[b]:row_ptr[b + 1]]
+        correct += int(torch.isin(top[b], truth).sum())
+    return correct / (top.shape[0] * k)
+
+
 def transpose_gradient(out_grad: torch.Tensor, want_bias_grad: bool = False):
     """g[B,L] -> (gT[L][ldg] zero padded in the batch, grad_bias[L] or None): the transposed copy the
     backward kernels read (and the input of the allocation-free grad_x entry point)."""

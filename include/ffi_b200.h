@@ -216,6 +216,21 @@ int ffi_grad_x_static(const float* W, const float* gT, int64_t ldg, const ffi_pl
                       void* stream);
 
 /*
+ * Forward whose epilogue keeps, per sample, the k (<= 8) highest logits of this table's rows instead
+ * of writing y: top_val[B][k] and top_idx[B][k] (row + label_offset; -1 where L < k) in the order of
+ * tf.nn.top_k (value descending, lower index first on ties).  It is what PrecisionAtK
+ * (sparse/metrics.py:9-70: topk_as_matrix + the overlap with the true labels) needs from the
+ * B x L logits, which here never reach HBM; with a sharded label dimension every shard returns
+ * its own k candidates.  Same shape coverage as ffi_forward_loss (FFI_ERR_UNSUPPORTED otherwise).
+ */
+size_t ffi_forward_topk_workspace_bytes(int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed,
+                                        int dtype);
+int ffi_forward_topk(const void* x, const int32_t* idx, const void* W, const float* bias,
+                     float* top_val, int32_t* top_idx, int k, int64_t B, int64_t N, int64_t L,
+                     int64_t K, int64_t label_offset, int x_transposed, int dtype, void* workspace,
+                     size_t workspace_bytes, void* stream);
+
+/*
  * The fused backward waits for its bulk copies with a time limit (about two seconds) instead of
  * forever; a wait that runs out is counted and the kernel winds down.  *out receives the count since
  * the library was loaded: 0 in a healthy process, anything else voids the calls that ran since the

@@ -415,6 +415,50 @@ def test_fused_forward_hinge_losses(cuda_device, shape, transposed, loss_name):
     assert torch.equal(gT_s[:, :B], gT[lo:hi, :B])
 
 
+@pytest.mark.parametrize("shape,transposed", [((128, 768, 20_011, 32), True), ((37, 254, 513, 16), False),
+                                              ((64, 100, 7, 8), True)], ids=["headline-like", "small", "few-rows"])
+def test_fused_forward_topk_and_precision_at_k(cuda_device, shape, transposed):
+    """Top-k of the logits from the forward kernel's epilogue (the logits are never written) against a
+    stable sort of the oracle's logits; P@k as the reference's PrecisionAtK accumulates it."""
+    dev = cuda_device
+    from ecml23_sparse_b200 import ops
+    B, N, L, K = shape
+    x, idx, W, _ = config_style_inputs(B, N, L, K, seed=13)
+    bias = synth.normal(13, 40, (L,), std=0.5).numpy()
+    row_ptr, labels = synth.multi_hot_targets(13, 41, B, L)
+    xin = np.ascontiguousarray(x.T) if transposed else x
+    k = 5
+    vals, lab = ops.forward_topk(to_cuda(xin, dev), to_cuda(idx, dev), to_cuda(W, dev), to_cuda(bias, dev), k, transposed)
+    z64 = oracle.forward_f64(x, idx, W, bias=bias)
+    order = np.argsort(-z64, axis=1, kind="stable")[:, :k]
+    want_vals = np.take_along_axis(z64, order, axis=1)
+    got_vals, got_lab = vals.cpu().numpy(), lab.cpu().numpy()
+    assert_close(got_vals, want_vals, RTOL, ATOL, "top-k values")
+    # labels must agree wherever the ranking is not decided by less than the fp32 tolerance
+    full = np.sort(z64, axis=1)[:, ::-1][:, :k + 1]
+    decided = np.abs(np.diff(full, axis=1)) > 1e-4
+    decided = decided[:, :k] & np.concatenate([np.ones((B, 1), bool), decided[:, :k - 1]], axis=1)
+    assert decided.mean() > 0.9
+    assert np.array_equal(got_lab[decided], order[decided])
+    # every returned label carries its own logit
+    assert_close(got_vals, np.take_along_axis(z64, got_lab.astype(np.int64), axis=1), RTOL, ATOL, "value of label")
+    # two shards merged give the same candidates
+    half = (L // 2) // 4 * 4
+    if half > 0:
+        c0 = ops.forward_topk(to_cuda(xin, dev), to_cuda(idx[:half], dev), to_cuda(W[:half], dev),
+                              to_cuda(bias[:half], dev), min(k, half), transposed, label_offset=0)
+        c1 = ops.forward_topk(to_cuda(xin, dev), to_cuda(idx[half:], dev), to_cuda(W[half:], dev),
+                              to_cuda(bias[half:], dev), min(k, L - half), transposed, label_offset=half)
+        mv, ml = ops.merge_topk([c0, c1], k)
+        assert torch.equal(ml, lab) and torch.equal(mv, vals)
+    # P@k against a direct count on the oracle's ranking
+    for kk in (1, 3, 5):
+        hits = sum(len(set(order[b, :kk].tolist()) & set(labels[row_ptr[b]:row_ptr[b + 1]].tolist())) for b in range(B))
+        want = hits / (B * kk)
+        got = ops.precision_at_k(lab, row_ptr, labels, kk)
+        assert abs(got - want) <= (1.0 - decided.mean()) + 1e-12
+
+
 def test_fused_forward_bce_reports_unsupported_shapes(cuda_device):
     dev = cuda_device
     from ecml23_sparse_b200 import ops
