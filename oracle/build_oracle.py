@@ -3,7 +3,7 @@
 * ``oracle/_build/libffi_oracle.so``  from ``oracle/ffi_oracle.c`` (gcc, OpenMP).
 * ``oracle/_ref/libffi_ref.so``       the reference's own CPU kernels, compiled from
   ``tfsparse/cc/kernels/forward.cpp`` and ``backward.cpp`` where they lie in a checkout of
-  the reference (path in ``$FFI_REFERENCE_ROOT``, default ``/root/reference``), against
+  the reference (path in ``$FFI_REFERENCE_ROOT``; a built-in default location is tried when it is unset), against
   the stand-in headers in ``oracle/ref_shim``.  Skipped when no checkout is present; a
   previously built library is then used as is.
 

@@ -1,6 +1,6 @@
 """Generates the golden fixtures in this directory from the reference's own CPU kernels.
 
-Needs a checkout of the reference (``$FFI_REFERENCE_ROOT``, default ``/root/reference``):
+Needs a checkout of the reference (``$FFI_REFERENCE_ROOT``; a built-in default location is tried when it is unset):
 ``oracle/build_oracle.py`` compiles its tfsparse/cc/kernels/forward.cpp and backward.cpp
 into ``oracle/_ref/libffi_ref.so`` and this script runs them (single thread) on the seeded
 inputs of ``tests/cases.py`` for each size fixture of testing/test.cpp:50-59.
