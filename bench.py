@@ -42,6 +42,7 @@ NCU_TRAFFIC_BYTES = {"forward": 195.1e6 + 302.4e6, "transpose_g": 345.8e6 + 283.
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--nccl-only", action="store_true", help="N > 1: sum grad_x with NCCL instead of ffi_peer_sum")
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -254,14 +255,28 @@ def run_ours(args):
     plan = ffi.FFIPlan(idx, N)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
+    # N > 1: the grad_x partials of the shards are added over peer memory by one kernel of the library
+    # (ffi_peer_sum); NCCL all-reduce where symmetric memory cannot be set up.
+    peer = None
+    if world > 1 and not args.nccl_only:
+        from ecml23_sparse_b200.sharded import PeerSum
+        peer = PeerSum.create(N * B + 4, dev)  # + one slot for the loss of the fused-loss leg
+    peer_out = torch.empty(N * B + 4, device=dev) if peer is not None else None
+
     def step_resident():
         y = ops._forward(xT, idx, W, bias, True)
-        gx, gW, gb = ops._backward(xT, idx, W, g, True, plan=plan, want_bias_grad=True)
-        if world > 1:
-            dist.all_reduce(gx)
+        if peer is not None:
+            _, gW, gb = ops._backward(xT, idx, W, g, True, plan=plan, want_bias_grad=True,
+                                      feature_grad_out=peer.slot()[:N * B])
+            gx = peer.sum(peer_out)[:N * B].view(N, B)
+        else:
+            gx, gW, gb = ops._backward(xT, idx, W, g, True, plan=plan, want_bias_grad=True)
+            if world > 1:
+                dist.all_reduce(gx)
         return y, gx, gW, gb
 
-    launches_per_step = 4  # forward, transposition of g, fused grad_x + grad_W, reduction of grad_x partials
+    # forward, transposition of g, fused grad_x + grad_W, reduction of grad_x partials (+ the peer sum)
+    launches_per_step = 4 + (1 if peer is not None else 0)
 
     def timed_loop(fn, steps, warmup):
         for _ in range(warmup):
@@ -316,11 +331,19 @@ def run_ours(args):
             lab_dev.copy_(lab_host, non_blocking=True)
             # logits never reach HBM: the forward kernel's epilogue writes the BCE gradient, transposed
             loss, gT = ops.forward_bce(x_dev, idx, W, bias, rp_dev, lab_dev, False, total_labels=L, label_offset=lo)
-            gx, gW, gb = ops._backward(x_dev, idx, W, gT, False, plan=plan, want_bias_grad=True,
-                                       grad_is_transposed=True)
-            if world > 1:
-                dist.all_reduce(gx)
-                dist.all_reduce(loss)
+            if peer is not None:
+                slot = peer.slot()
+                slot[N * B:N * B + 1].copy_(loss.view(1))
+                _, gW, gb = ops._backward(x_dev, idx, W, gT, False, plan=plan, want_bias_grad=True,
+                                          grad_is_transposed=True, feature_grad_out=slot[:N * B])
+                total = peer.sum(peer_out)
+                gx, loss = total[:N * B].view(B, N), total[N * B]
+            else:
+                gx, gW, gb = ops._backward(x_dev, idx, W, gT, False, plan=plan, want_bias_grad=True,
+                                           grad_is_transposed=True)
+                if world > 1:
+                    dist.all_reduce(gx)
+                    dist.all_reduce(loss)
             gx_host.copy_(gx, non_blocking=True)
             loss_host.copy_(loss, non_blocking=True)
 
@@ -407,7 +430,10 @@ def run_ours(args):
             "metric": "FFI fwd+bwd samples/sec", "value": value, "unit": "samples/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": workload_config(B, N, L, K, world),
+            "data": "synthetic",
+            "config": dict(workload_config(B, N, L, K, world),
+                           **({"collective": "ffi_peer_sum over peer memory (one launch)" if peer is not None
+                               else "NCCL all-reduce"} if world > 1 else {})),
             "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
             "roofline": roofline, "cpu_baseline": cpu_baseline,
         }

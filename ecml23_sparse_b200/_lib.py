@@ -36,7 +36,7 @@ EXPORTED_SYMBOLS = (
     "ffi_grad_x_static_max_scratch_bytes", "ffi_grad_x_static",
     "ffi_transposed_gradient_stride", "ffi_transpose_gradient",
     "ffi_backward_from_transposed", "ffi_forward_bce_workspace_bytes", "ffi_forward_bce", "ffi_forward_loss", "ffi_wait_timeouts",
-    "ffi_forward_topk_workspace_bytes", "ffi_forward_topk",
+    "ffi_forward_topk_workspace_bytes", "ffi_forward_topk", "ffi_peer_sum",
     "ffi_bce_workspace_bytes", "ffi_bce_grad", "ffi_adam_step",
 )
 
@@ -96,6 +96,8 @@ def _declare(lib):
     lib.ffi_forward_topk_workspace_bytes.argtypes = [i64, i64, i64, i64, i32, i32]
     lib.ffi_forward_topk.restype = i32
     lib.ffi_forward_topk.argtypes = [vp, vp, vp, vp, vp, vp, i32, i64, i64, i64, i64, i64, i32, i32, vp, sz, vp]
+    lib.ffi_peer_sum.restype = i32
+    lib.ffi_peer_sum.argtypes = [vp, vp, i32, i32, i64, ctypes.c_uint32, vp, vp]
     lib.ffi_wait_timeouts.restype = i32
     lib.ffi_wait_timeouts.argtypes = [vp]
     lib.ffi_bce_workspace_bytes.restype = sz

@@ -27,7 +27,9 @@
 #include "ffi_common.cuh"
 
 namespace ffi {
+int peer_wait_timeouts(int* out);  // peer_reduce.cu
 namespace {
+__device__ int g_wait_timeouts = 0;  // bounded waits of this file's kernels that gave up
 
 constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
@@ -412,7 +414,6 @@ __device__ __forceinline__ void tmem_wait_load(unsigned (&r)[8], unsigned (&s)[8
 }
 
 // ---- mbarrier + TMA (one tiled bulk copy per g tile, no multicast) ------------------------------
-__device__ int g_wait_timeouts = 0;  // bounded waits that gave up (read by ffi_wait_timeouts)
 
 __device__ __forceinline__ unsigned smem_u32(const void* ptr) {
     return static_cast<unsigned>(__cvta_generic_to_shared(ptr));
@@ -961,5 +962,9 @@ int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, floa
 extern "C" int ffi_wait_timeouts(int* out) {
     if (!out) return ffi::fail(FFI_ERR_INVALID_ARGUMENT, "NULL output passed to ffi_wait_timeouts");
     FFI_CUDA_CHECK(cudaMemcpyFromSymbol(out, ffi::g_wait_timeouts, sizeof(int)));
+    int peers = 0;
+    const int rc = ffi::peer_wait_timeouts(&peers);
+    if (rc != FFI_OK) return rc;
+    *out += peers;
     return FFI_OK;
 }

@@ -178,8 +178,11 @@ def _forward(features, lookup, weights, bias, transposed: bool) -> torch.Tensor:
 
 
 def _backward(features, lookup, weights, out_grad, transposed: bool, plan: Optional[FFIPlan] = None,
-              want_feature_grad=True, want_weight_grad=True, want_bias_grad=False, grad_is_transposed=False):
-    """grad_is_transposed: `out_grad` is gT[L][ldg] (from forward_bce / transpose_gradient), not g[B,L]."""
+              want_feature_grad=True, want_weight_grad=True, want_bias_grad=False, grad_is_transposed=False,
+              feature_grad_out: Optional[torch.Tensor] = None):
+    """grad_is_transposed: `out_grad` is gT[L][ldg] (from forward_bce / transpose_gradient), not g[B,L].
+    feature_grad_out: a contiguous float32 tensor with the number of elements of `features` that
+    receives grad_x instead of a fresh allocation (e.g. a slot of a peer-visible buffer)."""
     features = _check_cuda("features", features, _STORAGE_DTYPES)
     weights = _check_cuda("weights", weights, _STORAGE_DTYPES)
     dtype = _storage_dtype(features, weights)
@@ -195,7 +198,15 @@ def _backward(features, lookup, weights, out_grad, transposed: bool, plan: Optio
     dev = features.device
     if want_feature_grad and plan is None:
         plan = get_plan(lookup, N)
-    gx = torch.empty(features.shape, dtype=torch.float32, device=dev) if want_feature_grad else None
+    gx = None
+    if want_feature_grad:
+        if feature_grad_out is not None:
+            if (feature_grad_out.dtype != torch.float32 or not feature_grad_out.is_contiguous()
+                    or feature_grad_out.numel() != features.numel() or feature_grad_out.device != dev):
+                raise ValueError("feature_grad_out must be a contiguous float32 tensor of features' size on its device")
+            gx = feature_grad_out.view(features.shape)
+        else:
+            gx = torch.empty(features.shape, dtype=torch.float32, device=dev)
     gw = torch.empty(weights.shape, dtype=torch.float32, device=dev) if want_weight_grad else None
     gb = torch.empty((L,), dtype=torch.float32, device=dev) if want_bias_grad else None
     with torch.cuda.device(dev):

@@ -231,8 +231,21 @@ int ffi_forward_topk(const void* x, const int32_t* idx, const void* W, const flo
                      size_t workspace_bytes, void* stream);
 
 /*
- * The fused backward waits for its bulk copies with a time limit (about two seconds) instead of
- * forever; a wait that runs out is counted and the kernel winds down.  *out receives the count since
+ * Sum of the per-GPU grad_x partials of a label-sharded layer over peer memory, one launch per step
+ * (the small-message alternative to an all-reduce; no counterpart in the single-GPU reference).
+ * peer_bufs[r] / peer_flags[r] (host arrays of `world` device pointers) are rank r's buffer
+ * [2][n] floats and flag array [2][world] words as mapped into THIS process (e.g. the peer pointers
+ * of a symmetric allocation), flags zeroed once before the first step.  The caller has put its own
+ * partial of this step into peer_bufs[rank] + (step & 1) * n on `stream`; `step` counts 1, 2, 3, ...
+ * and is the same on all ranks.  out[n] receives the sum in rank order (identical bits on all ranks).
+ * Waits on other ranks are bounded (see ffi_wait_timeouts).
+ */
+int ffi_peer_sum(const void* const* peer_bufs, void* const* peer_flags, int rank, int world,
+                 int64_t n, uint32_t step, float* out, void* stream);
+
+/*
+ * The fused backward waits for its bulk copies, and ffi_peer_sum for the other GPUs, with a time
+ * limit (about two seconds) instead of forever; a wait that runs out is counted and the kernel winds down.  *out receives the count since
  * the library was loaded: 0 in a healthy process, anything else voids the calls that ran since the
  * last check.  Synchronises the device.  No counterpart in the reference.
  */
