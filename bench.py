@@ -42,7 +42,10 @@ NCU_TRAFFIC_BYTES = {"forward": 195.1e6 + 302.4e6, "transpose_g": 345.8e6 + 283.
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--nccl-only", action="store_true", help="N > 1: sum grad_x with NCCL instead of ffi_peer_sum")
+    ap.add_argument("--collective", choices=["auto", "nccl", "peer"], default="auto",
+                    help="N > 1: how the shards' grad_x partials are summed. auto = NCCL all-reduce in the resident "
+                         "leg and ffi_peer_sum (grad_x and loss in one launch) in the end-to-end leg, the faster "
+                         "choice for each at 8 GPUs")
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -258,14 +261,14 @@ def run_ours(args):
     # N > 1: the grad_x partials of the shards are added over peer memory by one kernel of the library
     # (ffi_peer_sum); NCCL all-reduce where symmetric memory cannot be set up.
     peer = None
-    if world > 1 and not args.nccl_only:
+    if world > 1 and args.collective != "nccl":
         from ecml23_sparse_b200.sharded import PeerSum
         peer = PeerSum.create(N * B + 4, dev)  # + one slot for the loss of the fused-loss leg
     peer_out = torch.empty(N * B + 4, device=dev) if peer is not None else None
 
     def step_resident():
         y = ops._forward(xT, idx, W, bias, True)
-        if peer is not None:
+        if peer is not None and args.collective == "peer":
             _, gW, gb = ops._backward(xT, idx, W, g, True, plan=plan, want_bias_grad=True,
                                       feature_grad_out=peer.slot()[:N * B])
             gx = peer.sum(peer_out)[:N * B].view(N, B)
@@ -276,7 +279,7 @@ def run_ours(args):
         return y, gx, gW, gb
 
     # forward, transposition of g, fused grad_x + grad_W, reduction of grad_x partials (+ the peer sum)
-    launches_per_step = 4 + (1 if peer is not None else 0)
+    launches_per_step = 4 + (1 if peer is not None and args.collective == "peer" else 0)
 
     def timed_loop(fn, steps, warmup):
         for _ in range(warmup):
@@ -432,8 +435,10 @@ def run_ours(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": dict(workload_config(B, N, L, K, world),
-                           **({"collective": "ffi_peer_sum over peer memory (one launch)" if peer is not None
-                               else "NCCL all-reduce"} if world > 1 else {})),
+                           **({"collective": {"resident": "ffi_peer_sum" if peer is not None and args.collective == "peer"
+                                              else "NCCL all-reduce",
+                                              "e2e": "ffi_peer_sum (grad_x + loss, one launch)" if peer is not None
+                                              else "NCCL all-reduce"}} if world > 1 else {})),
             "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
             "roofline": roofline, "cpu_baseline": cpu_baseline,
         }

@@ -68,6 +68,8 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
             gw = oracle.grad_w_f32(xT_.numpy(), idx_s, g_s.numpy(), transposed=True)
             return torch.from_numpy(gx), torch.from_numpy(gw), torch.from_numpy(g_s.numpy().sum(0))
 
+        # no symmetric (peer-visible) memory on CPU ranks: all ranks agree to keep the all-reduce
+        assert sharded.PeerSum.create(N * B, torch.device("cpu")) is None
         step = sharded.LabelShardedStep(forward_fn, backward_fn)
         assert step.world == world
         y, gx, gW, gb = step.step(xT, lambda y_: g[:, lo:hi].contiguous())
