@@ -425,7 +425,7 @@ def run_ours(args):
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cb = time_cpu_reference(B, N, L, K, steps=8, warmup=1, budget_s=20.0)
+        cb = time_cpu_reference(B, N, L, K, steps=64, warmup=2, budget_s=20.0)  # about 10-20 s of CPU work
         cpu_baseline = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
 
     if rank == 0:
