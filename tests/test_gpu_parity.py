@@ -277,6 +277,63 @@ def test_layer_module_matches_oracle(cuda_device):
     assert_close(layer.bias.grad.cpu().numpy(), oracle.grad_bias_f64(g), RTOL, ATOL, "layer grad_bias")
 
 
+def test_two_layer_stack_with_fused_loss_and_adam(cuda_device):
+    """The shape family of the benchmark configurations 1 and 2, scaled down: an FFI layer with ReLU
+    feeding the FFI output layer, loss fused into the output layer's forward, one Adam step on the
+    output weights; every gradient against the fp64 oracle chained by hand."""
+    dev = cuda_device
+    from ecml23_sparse_b200 import ops
+    B, N0, N1, L, K = 128, 768, 512, 6_001, 32  # hidden width that keeps the output layer on the fused-loss path
+    x0 = synth.normal(21, 0, (B, N0)).numpy()
+    idx1 = synth.indices_without_replacement(21, 1, N1, K, N0).numpy()
+    W1 = synth.normal(21, 2, (N1, K), std=(2.0 / K) ** 0.5).numpy()
+    idx2 = synth.indices_without_replacement(21, 3, L, K, N1).numpy()
+    W2 = synth.normal(21, 4, (L, K), std=(2.0 / K) ** 0.5).numpy()
+    bias2 = np.zeros(L, np.float32)
+    row_ptr, labels = synth.multi_hot_targets(21, 5, B, L)
+
+    # device: hidden = relu(FFI1(x0)); (loss, gT) = FFI2 with the fused BCE; backward through both
+    xd = to_cuda(x0, dev)
+    h_pre = ops._forward(xd, to_cuda(idx1, dev), to_cuda(W1, dev), None, False)
+    h = torch.relu(h_pre)
+    loss, gT = ops.forward_bce(h, to_cuda(idx2, dev), to_cuda(W2, dev), to_cuda(bias2, dev), row_ptr, labels, False)
+    gh, gW2, gb2 = ops._backward(h, to_cuda(idx2, dev), to_cuda(W2, dev), gT, False, want_bias_grad=True,
+                                 grad_is_transposed=True)
+    gh_pre = gh * (h_pre > 0)
+    gx0, gW1, _ = ops._backward(xd, to_cuda(idx1, dev), to_cuda(W1, dev), gh_pre.contiguous(), False)
+
+    # oracle chain in fp64 (the hidden activations the device produced are the second layer's input)
+    h_ref = np.maximum(oracle.forward_f64(x0, idx1, W1), 0.0)
+    assert_close(h.cpu().numpy(), h_ref, RTOL, ATOL, "hidden activations")
+    h32 = h.cpu().numpy()
+    z = oracle.forward_f64(h32, idx2, W2, bias=bias2).astype(np.float32)
+    loss_ref, g_ref = oracle.bce_f64(z, row_ptr.numpy(), labels.numpy())
+    assert abs(float(loss) - loss_ref) <= 2e-5 * abs(loss_ref) + 1e-7
+    g32 = g_ref.astype(np.float32)
+    scale = np.abs(g32).max()
+
+    def close(name, got, want, rtol=2e-4):
+        err = np.abs(got.cpu().numpy().astype(np.float64) - want).max()
+        assert err <= rtol * np.abs(want).max() + 1e-12, f"{name}: {err:.3e} vs scale {np.abs(want).max():.3e}"
+
+    close("grad_W2", gW2, oracle.grad_w_f64(h32, idx2, g32))
+    close("grad_bias2", gb2, oracle.grad_bias_f64(g32))
+    gh_ref = oracle.grad_x_f64(idx2, W2, g32, N1)
+    close("grad_hidden", gh, gh_ref)
+    ghp = (gh.cpu().numpy() * (h_pre.cpu().numpy() > 0)).astype(np.float32)
+    close("grad_W1", gW1, oracle.grad_w_f64(x0, idx1, ghp))
+    close("grad_x0", gx0, oracle.grad_x_f64(idx1, W1, ghp, N0))
+    assert scale > 0
+
+    # one Adam step on the output layer's weights (lr 1e-3, beta 0.9/0.999, eps 1e-7, as Keras)
+    w = to_cuda(W2, dev).reshape(-1).clone()
+    opt = ffi.FusedAdam([w], lr=1e-3)
+    opt.step([gW2.reshape(-1)])
+    w_ref, _, _ = oracle.adam_f64(W2.reshape(-1), np.zeros(L * K), np.zeros(L * K), gW2.cpu().numpy().reshape(-1),
+                                  np.float32(1e-3), np.float32(0.9), np.float32(0.999), np.float32(1e-7), 1)
+    assert_close(w.cpu().numpy(), w_ref, 1e-5, 1e-6, "Adam step")
+
+
 def _torch_reference(xT, idx, W, g, chunk=4096):
     """Plain PyTorch fp64 statement of the layer, chunked over the outputs: (y, grad_x[N,B], grad_W)."""
     N, B = xT.shape
