@@ -398,7 +398,11 @@ def run_ours(args):
         "transpose_g": (8 * B * Ls + 4 * Ls, 0),
         "backward_fused": (4 * B * Ls + 8 * Ls * K + 4 * Ls * K + 8 * B * N, 2 * fma_pass),
     }
-    names = {"forward": "ffi_fwd_pair_kernel", "transpose_g": "transpose_g_kernel", "backward_fused": "ffi_bwd_pairs_kernel" if B > 64 else "ffi_bwd_fused_kernel"}
+    narrow = N <= 2048  # the plan holds the chunked index the one-pass backward walks; x tiles fit shared memory
+    names = {"forward": "ffi_fwd_pair_kernel" if narrow else "ffi_fwd_kernel",
+             "transpose_g": "transpose_g_kernel",
+             "backward_fused": ("ffi_bwd_pairs_kernel" if B > 64 else "ffi_bwd_fused_kernel") if narrow
+             else "ffi_grad_w_kernel + ffi_grad_x_wide_kernel"}
     kernels = {}
     for name, ms in kernel_ms.items():
         nbytes, fmas = work[name]
