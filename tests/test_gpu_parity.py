@@ -334,6 +334,35 @@ def test_two_layer_stack_with_fused_loss_and_adam(cuda_device):
     assert_close(w.cpu().numpy(), w_ref, 1e-5, 1e-6, "Adam step")
 
 
+def test_peer_sum_single_rank_and_argument_checks(cuda_device):
+    """ffi_peer_sum with a world of one rank (the multi-GPU exchange needs several GPUs; here the
+    kernel's flag protocol and the sum run against the rank's own buffers) and its argument checks."""
+    import ctypes
+
+    dev = cuda_device
+    lib = _lib.load()
+    n = 768 * 128 + 4
+    buf = torch.zeros((2, n), device=dev)
+    flags = torch.zeros((2, 1), dtype=torch.int32, device=dev)
+    out = torch.empty(n, device=dev)
+    bufs = (ctypes.c_void_p * 1)(buf.data_ptr())
+    flgs = (ctypes.c_void_p * 1)(flags.data_ptr())
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    for step in range(1, 6):
+        part = torch.randn(n, device=dev)
+        buf[step & 1].copy_(part)
+        _lib.check(lib.ffi_peer_sum(bufs, flgs, 0, 1, n, step, out.data_ptr(), stream))
+        assert torch.equal(out, part)
+        assert int(flags[step & 1, 0]) == step
+    assert lib.ffi_peer_sum(bufs, flgs, 0, 1, n, 0, out.data_ptr(), stream) == 1      # steps count from 1
+    assert lib.ffi_peer_sum(bufs, flgs, 1, 1, n, 1, out.data_ptr(), stream) == 1      # rank outside the world
+    assert lib.ffi_peer_sum(bufs, flgs, 0, 1, n - 1, 1, out.data_ptr(), stream) == 1  # not a multiple of 4
+    assert lib.ffi_peer_sum(None, flgs, 0, 1, n, 1, out.data_ptr(), stream) == 1
+    count = ctypes.c_int(-1)
+    _lib.check(lib.ffi_wait_timeouts(ctypes.byref(count)))
+    assert count.value == 0
+
+
 def _torch_reference(xT, idx, W, g, chunk=4096):
     """Plain PyTorch fp64 statement of the layer, chunked over the outputs: (y, grad_x[N,B], grad_W)."""
     N, B = xT.shape
