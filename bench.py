@@ -244,6 +244,9 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # NCCL announces its version on stdout at the VERSION debug level; stdout carries the JSON line
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
     B, N, L, K = args.batch, args.n_in, args.units, args.fan_in
     lo, hi = sharded.shard_range(L, world, rank)
