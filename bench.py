@@ -42,10 +42,11 @@ NCU_TRAFFIC_BYTES = {"forward": 195.1e6 + 302.4e6, "transpose_g": 345.8e6 + 283.
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--collective", choices=["auto", "nccl", "peer"], default="auto",
-                    help="N > 1: how the shards' grad_x partials are summed. auto = NCCL all-reduce in the resident "
-                         "leg and ffi_peer_sum (grad_x and loss in one launch) in the end-to-end leg, the faster "
-                         "choice for each at 8 GPUs")
+    ap.add_argument("--collective", choices=["auto", "nccl", "peer", "multimem"], default="auto",
+                    help="N > 1: how the shards' grad_x partials are summed in the resident leg: nccl, peer "
+                         "(ffi_peer_sum) or multimem (torch's in-switch all-reduce on the symmetric buffer); auto = "
+                         "multimem from 4 GPUs on, else NCCL.  The end-to-end leg uses ffi_peer_sum (grad_x and loss "
+                         "in one launch) unless nccl is asked for")
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -279,9 +280,32 @@ def run_ours(args):
         peer = PeerSum.create(N * B + 4, dev)  # + one slot for the loss of the fused-loss leg
     peer_out = torch.empty(N * B + 4, device=dev) if peer is not None else None
 
+    # Exchange of the resident leg.  Measured at 8 GPUs (samples/s): in-switch all-reduce 518k, NCCL 491k,
+    # ffi_peer_sum 479k; at 2 GPUs all three are equal.  auto = the in-switch one from 4 GPUs on when a
+    # trial call works on every rank, else NCCL.
+    resident_mode = "nccl"
+    if peer is not None and args.collective == "peer":
+        resident_mode = "peer"
+    elif peer is not None and (args.collective == "multimem" or (args.collective == "auto" and world >= 4)):
+        ok = torch.ones(1, device=dev)
+        try:
+            torch.ops.symm_mem.multimem_all_reduce_(peer.buf[0], "sum", dist.group.WORLD.group_name)
+            torch.cuda.synchronize()
+        except Exception:  # noqa: BLE001 - no multicast support here
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 1:
+            resident_mode = "multimem"
+
     def step_resident():
         y = ops._forward(xT, idx, W, bias, True)
-        if peer is not None and args.collective == "peer":
+        if resident_mode == "multimem":
+            slot = peer.buf[0]
+            _, gW, gb = ops._backward(xT, idx, W, g, True, plan=plan, want_bias_grad=True,
+                                      feature_grad_out=slot[:N * B])
+            torch.ops.symm_mem.multimem_all_reduce_(slot, "sum", dist.group.WORLD.group_name)
+            gx = slot[:N * B].view(N, B)
+        elif resident_mode == "peer":
             _, gW, gb = ops._backward(xT, idx, W, g, True, plan=plan, want_bias_grad=True,
                                       feature_grad_out=peer.slot()[:N * B])
             gx = peer.sum(peer_out)[:N * B].view(N, B)
@@ -292,7 +316,7 @@ def run_ours(args):
         return y, gx, gW, gb
 
     # forward, transposition of g, fused grad_x + grad_W, reduction of grad_x partials (+ the peer sum)
-    launches_per_step = 4 + (1 if peer is not None and args.collective == "peer" else 0)
+    launches_per_step = 4 + (1 if resident_mode == "peer" else 0)
 
     def timed_loop(fn, steps, warmup):
         for _ in range(warmup):
@@ -452,8 +476,9 @@ def run_ours(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": dict(workload_config(B, N, L, K, world),
-                           **({"collective": {"resident": "ffi_peer_sum" if peer is not None and args.collective == "peer"
-                                              else "NCCL all-reduce",
+                           **({"collective": {"resident": {"peer": "ffi_peer_sum", "nccl": "NCCL all-reduce",
+                                                           "multimem": "in-switch (NVLS) all-reduce of torch symmetric memory"
+                                                           }[resident_mode],
                                               "e2e": "ffi_peer_sum (grad_x + loss, one launch)" if peer is not None
                                               else "NCCL all-reduce"}} if world > 1 else {})),
             "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
