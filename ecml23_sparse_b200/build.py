@@ -43,10 +43,39 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+OBJ_DIR = os.path.join(PKG_DIR, "build")
+
+
+def _compile_one(args) -> str:
+    src, obj, extra, verbose = args
+    cmd = [_nvcc(), *NVCC_FLAGS, "-c", "-I", INCLUDE, "-I", CSRC, *extra, src, "-o", obj]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    subprocess.run(cmd, check=True)
+    return obj
+
+
 def build(force: bool = False, verbose: bool = False, extra: list[str] | None = None) -> str:
+    """Compiles every source file to an object (in parallel; an object is reused while it is newer than
+    its source and the shared headers) and links them into the shared library."""
     if not force and not _stale():
         return LIB_PATH
-    cmd = [_nvcc(), *NVCC_FLAGS, "-shared", "-I", INCLUDE, "-I", CSRC, *(extra or []), *sources(), "-o", LIB_PATH]
+    from concurrent.futures import ThreadPoolExecutor
+
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(INCLUDE, "*.h"))
+    newest_header = max((os.path.getmtime(h) for h in headers), default=0.0)
+    jobs, objs = [], []
+    for src in sources():
+        obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
+        objs.append(obj)
+        fresh = (not force and not extra and os.path.exists(obj)
+                 and os.path.getmtime(obj) > max(os.path.getmtime(src), newest_header))
+        if not fresh:
+            jobs.append((src, obj, extra or [], verbose))
+    with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as pool:
+        list(pool.map(_compile_one, jobs))
+    cmd = [_nvcc(), *NVCC_FLAGS, "-shared", *objs, "-o", LIB_PATH]
     if verbose:
         print(" ".join(cmd), flush=True)
     subprocess.run(cmd, check=True)

@@ -49,6 +49,16 @@ int get_device_info(DeviceInfo* info) {
     return FFI_OK;
 }
 
+// A plan's index arrays live on the GPU it was built on: a call made with another GPU current would
+// hand its kernels pointers into that other GPU's memory.
+int check_plan_device(const ffi_plan* plan) {
+    int dev = -1;
+    FFI_CUDA_CHECK(cudaGetDevice(&dev));
+    if (plan && plan->device != dev)
+        return fail(FFI_ERR_STALE_PLAN, "plan was built on device %d, the current device is %d", plan->device, dev);
+    return FFI_OK;
+}
+
 bool forward_uses_smem_x(int B, int N, int K, int* bpl_out);
 int launch_widen_bf16(const void* src, float* dst, int64_t n, cudaStream_t stream);
 bool grad_w_uses_smem_x(int B, int N, int K, int* bpl_out);
@@ -246,6 +256,8 @@ static int backward_impl(const void* x, const int32_t* idx, const void* W, const
             return fail(FFI_ERR_STALE_PLAN, "plan was built for (L,K,N)=(%lld,%lld,%lld), call has (%lld,%lld,%lld)",
                         (long long)plan->L, (long long)plan->K, (long long)plan->N, (long long)L, (long long)K,
                         (long long)N);
+        rc = check_plan_device(plan);
+        if (rc != FFI_OK) return rc;
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     unsigned char* ws = static_cast<unsigned char*>(workspace);

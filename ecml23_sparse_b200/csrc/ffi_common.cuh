@@ -126,6 +126,9 @@ struct ffi_plan {
 
 namespace ffi {
 
+// FFI_ERR_STALE_PLAN unless `plan` was built on the current device.
+int check_plan_device(const ffi_plan* plan);
+
 struct GradXArgs {
     const int32_t* idx;
     const float* W;

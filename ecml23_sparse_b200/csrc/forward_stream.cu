@@ -37,6 +37,7 @@ struct FwdStreamParams {
 };
 
 constexpr int kTopK = 8;  // capacity of a top-k list (P@1, P@3, P@5 need 5)
+constexpr size_t kMaxLossPartials = 1024;  // doubles the caller's scratch holds for the per-CTA loss sums
 
 // Sorted (value descending, row ascending) insertion; `better` orders candidates the way
 // tf.nn.top_k does: higher value first, lower index on ties.
@@ -301,11 +302,17 @@ int launch_pair_t(const FwdStreamParams& p, size_t smem, int nBT, const DeviceIn
     int occ = 0;
     FFI_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kThreads, smem));
     if (occ < 1) return fail(FFI_ERR_CUDA, "streaming forward kernel does not fit on an SM (smem %zu)", smem);
+    // The epilogue variants write one record per CTA (loss partial, top-k lists) into scratch that is
+    // sized for one CTA per SM, whatever occupancy the kernel would allow.
+    if (MODE != 0) occ = 1;
     int per_bt = dev.sm_count * occ / nBT;
     if (per_bt < 1) per_bt = 1;
     const long long numQuads = (static_cast<long long>(p.L) + 3) / 4;
     const long long want = (numQuads + kWarps - 1) / kWarps;
     dim3 grid(static_cast<unsigned>(want < per_bt ? want : per_bt), static_cast<unsigned>(nBT));
+    if (MODE == 1 && static_cast<size_t>(grid.x) * grid.y > kMaxLossPartials)
+        return fail(FFI_ERR_UNSUPPORTED, "the fused loss keeps at most %zu per-CTA partials; this batch needs %u",
+                    kMaxLossPartials, grid.x * grid.y);
     if (ctas_out) *ctas_out = static_cast<int>(grid.x * grid.y);
     kern<<<grid, kThreads, smem, stream>>>(p);
     FFI_LAUNCH_CHECK("ffi_fwd_pair_kernel");

@@ -483,8 +483,12 @@ extern "C" int ffi_grad_x_static(const float* W, const float* gT, int64_t ldg, c
         return fail(FFI_ERR_STALE_PLAN, "plan was built for (L,K,N)=(%lld,%lld,%lld), call has (%lld,%lld,%lld)",
                     (long long)plan->L, (long long)plan->K, (long long)plan->N, (long long)L, (long long)K,
                     (long long)N);
-    if (ldg < B || ldg % 32 != 0 || reinterpret_cast<uintptr_t>(gT) % 16 != 0)
-        return fail(FFI_ERR_INVALID_ARGUMENT, "gT must be 16-byte aligned with a row stride that is a multiple of 32 and >= B");
+    int rc = check_plan_device(plan);
+    if (rc != FFI_OK) return rc;
+    if (ldg < transposed_g_stride(B) || ldg % 32 != 0 || reinterpret_cast<uintptr_t>(gT) % 16 != 0)
+        return fail(FFI_ERR_INVALID_ARGUMENT,
+                    "gT must be 16-byte aligned with a row stride that is a multiple of 32 and >= "
+                    "ffi_transposed_gradient_stride(B) = %lld", (long long)transposed_g_stride(B));
     const size_t need = grad_x_workspace_bytes(plan, B);
     if (need > kStaticScratchBytes)
         return fail(FFI_ERR_WORKSPACE,
@@ -492,7 +496,7 @@ extern "C" int ffi_grad_x_static(const float* W, const float* gT, int64_t ldg, c
                     "use ffi_backward with a caller workspace",
                     need, kStaticScratchBytes);
     void* scratch = nullptr;
-    int rc = static_scratch_address(&scratch);
+    rc = static_scratch_address(&scratch);
     if (rc != FFI_OK) return rc;
     GradXArgs a;
     a.idx = nullptr;

@@ -261,15 +261,20 @@ extern "C" int ffi_plan_create(const int32_t* idx, int64_t L, int64_t K, int64_t
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const long long n = L * K;
 
-    ffi_plan* plan = new ffi_plan();
+    // Owns the half-built plan: every early return below (the CUDA check macros included) frees
+    // the plan and its device arrays; success hands it to the caller.
+    struct PlanOwner {
+        ffi_plan* p;
+        ~PlanOwner() {
+            if (p) ffi_plan_destroy(p);
+        }
+    } owner{new ffi_plan()};
+    ffi_plan* plan = owner.p;
     plan->L = L;
     plan->K = K;
     plan->N = N;
     FFI_CUDA_CHECK(cudaGetDevice(&plan->device));
-    auto cleanup = [&](int rc) {
-        ffi_plan_destroy(plan);
-        return rc;
-    };
+    auto cleanup = [&](int rc) { return rc; };
 
     if (cudaMalloc(&plan->rowptr, (N + 1) * sizeof(int)) != cudaSuccess ||
         cudaMalloc(&plan->perm, n * sizeof(int)) != cudaSuccess) {
@@ -356,6 +361,7 @@ extern "C" int ffi_plan_create(const int32_t* idx, int64_t L, int64_t K, int64_t
         plan->has_chunks = true;
     }
     FFI_CUDA_CHECK(cudaStreamSynchronize(stream));
+    owner.p = nullptr;
     *out_plan = plan;
     return FFI_OK;
 }

@@ -193,9 +193,11 @@ int ffi_forward_loss(int loss_kind, const void* x, const int32_t* idx, const voi
  * partial sums) lives in a fixed __device__ array inside the library: 20 MiB
  * (ffi_grad_x_static_max_scratch_bytes()), held by every GPU that loads the library until the
  * process exits.  The call performs no cudaMalloc/cudaFree and calls no allocating routine.
+ * The plan must have been built on the device that is current at the call (FFI_ERR_STALE_PLAN).
  *
  * Inputs: W[L,K]; gT, the upstream gradient ALREADY transposed to [L][ldg] (batch contiguous,
- * ldg a multiple of 32 and >= B, columns B..ldg-1 zero, 16-byte aligned) - the transposed copy
+ * ldg a multiple of 32 and >= ffi_transposed_gradient_stride(B), columns B..ldg-1 zero, 16-byte
+ * aligned) - the transposed copy
  * that ffi_backward builds inside its workspace is an input here; the plan of idx.
  * Output: grad_x in the layout of x ([N,B] when x_transposed, else [B,N]).
  *
@@ -204,7 +206,10 @@ int ffi_forward_loss(int loss_kind, const void* x, const int32_t* idx, const voi
  *    bytes; the headline shape B=128, N=768 needs 18.4 MiB) are refused with FFI_ERR_WORKSPACE;
  *    use ffi_backward with a caller workspace for those;
  *  - the first call on each device looks up the array's device address
- *    (cudaGetSymbolAddress): make that first call before starting any stream capture;
+ *    (cudaGetSymbolAddress): make that first call before starting any stream capture.  With lazy
+ *    module loading (the CUDA default) that lookup is also the moment the driver loads the module
+ *    and sets the 20 MiB aside on that device, so the "no allocation" property holds for every call
+ *    after the first one on a device, and the first one is the place to take that one-time cost;
  *  - all calls on a device share the one array, so two calls that may overlap on the GPU
  *    (different streams) race with each other: serialise them.  The array keeps the previous
  *    call's contents; nothing has to be cleared because every word a call reads it has

@@ -41,7 +41,9 @@ def build_oracle(force: bool = False) -> str:
 
 
 def reference_root() -> str:
-    return os.environ.get("FFI_REFERENCE_ROOT", "/root/reference")
+    """Checkout of the reference: $FFI_REFERENCE_ROOT, else a `reference` directory beside this repository."""
+    beside = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return os.environ.get("FFI_REFERENCE_ROOT", beside)
 
 
 def build_reference(force: bool = False) -> str | None:

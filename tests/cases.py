@@ -32,6 +32,21 @@ KAT_W = np.array([[1, 2], [3, 4]], np.float32)
 KAT_Y = np.array([[8, 15], [17, 36], [3, 4]], np.float32)
 
 
+# fp32 results against the fp64 oracle: |d| <= ATOL + RTOL*|ref|
+RTOL = 1e-5
+ATOL = 1e-5
+
+
+def gx_atol(L, K, N):
+    """Absolute floor for grad_x.  grad_x[b,i] sums n = L*K/N products; the rounding error of any
+    fp32 summation grows like sqrt(n) times the size of the partial sums, independently of how
+    close to zero the total lands, so the 1e-5 floor (meant for O(1) sums) is widened by
+    sqrt(n)/32 once n exceeds 1024.  The reference's own fp32 running sum is further from the fp64
+    value than this (checked on the 4,000,000-unit fixture in test_gpu_parity.py)."""
+    n = L * K / N
+    return ATOL * max(1.0, n ** 0.5 / 32.0)
+
+
 def size_id(size) -> str:
     return "B{}_N{}_L{}_K{}".format(*size)
 

@@ -13,24 +13,10 @@ import torch
 import oracle
 import ecml23_sparse_b200 as ffi
 from ecml23_sparse_b200 import _lib, synth
-from cases import (HUGE_SIZE, KAT_IDX, KAT_W, KAT_X, KAT_Y, SMALL_SIZES, assert_close, config_style_inputs,
-                   golden_path, reference_style_inputs, size_id, to_cuda)
+from cases import (ATOL, HUGE_SIZE, KAT_IDX, KAT_W, KAT_X, KAT_Y, RTOL, SMALL_SIZES, assert_close, config_style_inputs,
+                   golden_path, gx_atol, reference_style_inputs, size_id, to_cuda)
 
 pytestmark = pytest.mark.gpu
-
-RTOL = 1e-5
-ATOL = 1e-5
-
-
-def gx_atol(L, K, N):
-    """Absolute floor for grad_x.  grad_x[b,i] sums n = L*K/N products; the rounding error of any
-    fp32 summation grows like sqrt(n) times the size of the partial sums, independently of how
-    close to zero the total lands, so the 1e-5 floor (meant for O(1) sums) is widened by
-    sqrt(n)/32 once n exceeds 1024.  The reference's own fp32 running sum is further from the fp64
-    value than this (checked on the 4,000,000-unit fixture below)."""
-    n = L * K / N
-    return ATOL * max(1.0, n ** 0.5 / 32.0)
-
 
 def run_forward(dev, x, idx, W, transposed, bias=None):
     xin = np.ascontiguousarray(x.T) if transposed else x

@@ -14,9 +14,11 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 import ecml23_sparse_b200 as ffi
 from ecml23_sparse_b200 import _lib, synth
 from ecml23_sparse_b200.ops import _backward, _stream_ptr
+from cases import RTOL, assert_close, gx_atol
 
 pytestmark = pytest.mark.gpu
 
@@ -39,7 +41,9 @@ def _static_grad_x(W, gT, plan, B, N, L, K, transposed):
     return out
 
 
-@pytest.mark.parametrize("shape,transposed", [((128, 768, 20_011, 32), True), ((37, 254, 513, 16), False)])
+@pytest.mark.parametrize("shape,transposed", [((128, 768, 20_011, 32), True), ((37, 254, 513, 16), False),
+                                              ((16, 5_000, 3_000, 8), False), ((200, 300, 2_000, 12), True)],
+                         ids=["headline-like", "small", "wide-inputs", "two-batch-tiles"])
 def test_static_scratch_grad_x_matches_regular_entry_point_twice(cuda_device, shape, transposed):
     dev = cuda_device
     B, N, L, K = shape
@@ -56,6 +60,10 @@ def test_static_scratch_grad_x_matches_regular_entry_point_twice(cuda_device, sh
         # which is well inside the 1e-5 tolerance the other grad_x tests use
         assert torch.allclose(got, expected, rtol=1e-5, atol=1e-5)
         assert torch.equal(got, expected)
+        # and the numbers themselves against the CPU oracle (fp64), independent of any CUDA kernel
+        want = oracle.grad_x_f64(idx.cpu().numpy(), W.cpu().numpy(), g.cpu().numpy(), N)
+        got_bn = got.t() if transposed else got
+        assert_close(got_bn.cpu().numpy(), want, RTOL, gx_atol(L, K, N), "static-scratch grad_x vs oracle")
 
 
 def test_static_scratch_rejects_oversize_and_bad_arguments(cuda_device):
