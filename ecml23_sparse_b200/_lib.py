@@ -38,6 +38,7 @@ EXPORTED_SYMBOLS = (
     "ffi_backward_from_transposed", "ffi_forward_bce_workspace_bytes", "ffi_forward_bce", "ffi_forward_loss", "ffi_wait_timeouts",
     "ffi_forward_topk_workspace_bytes", "ffi_forward_topk", "ffi_peer_sum",
     "ffi_bce_workspace_bytes", "ffi_bce_grad", "ffi_adam_step",
+    "ffi_rewire_workspace_bytes", "ffi_rewire",
 )
 
 
@@ -104,6 +105,10 @@ def _declare(lib):
     lib.ffi_bce_workspace_bytes.argtypes = [i64, i64]
     lib.ffi_bce_grad.restype = i32
     lib.ffi_bce_grad.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, sz, vp]
+    lib.ffi_rewire_workspace_bytes.restype = sz
+    lib.ffi_rewire_workspace_bytes.argtypes = []
+    lib.ffi_rewire.restype = i32
+    lib.ffi_rewire.argtypes = [vp, vp, vp, vp, i64, i64, i64, ctypes.c_uint64, vp, vp, vp, sz, vp]
     lib.ffi_adam_step.restype = i32
     lib.ffi_adam_step.argtypes = [vp, vp, vp, vp, i64, f32, f32, f32, f32, i64, i32, vp]
 

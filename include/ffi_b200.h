@@ -284,6 +284,26 @@ int ffi_bce_grad(const float* z, const int32_t* row_ptr, const int32_t* labels, 
 int ffi_adam_step(void* w, float* m, float* v, const float* grad, int64_t n, float lr, float beta1,
                   float beta2, float eps, int64_t step, int dtype, void* stream);
 
+/* --------------------------------------------------------------- rewiring ---- */
+
+/*
+ * One rewiring step on the flat arrays of a layer (n = L*K connections), entirely on the device:
+ *   threshold = the num_selected-th smallest |w|  (FixedFractionSelector.select, sparse/layer.py:62-86,
+ *               where num_selected = round(fraction * n) is computed by the caller);
+ *   every position p with |w[p]| < threshold (strictly, as tf.less) is rewired:
+ *     idx[p] = a new source uniform in [0, n_in) (StratifiedRewireLayerV2._rewire,
+ *              sparse/custom_layer.py:32-43; here splitmix64 of (seed, p), bits >> 1, mod n_in),
+ *     m[p] = v[p] = 0 when the Adam moments are given (custom_layer.py:20-30, sparse/optimizer.py:14-23);
+ *   w is not modified.
+ * *threshold_out (device float) and *count_out (device int32, the number of rewired positions) may be
+ * NULL.  num_selected = 0 rewires nothing.  idx changed: build a new plan before the next backward.
+ * Workspace: ffi_rewire_workspace_bytes() bytes, 16-byte aligned.  No host synchronisation.
+ */
+size_t ffi_rewire_workspace_bytes(void);
+int ffi_rewire(const float* w, int32_t* idx, float* m, float* v, int64_t n, int64_t n_in, int64_t num_selected,
+               uint64_t seed, float* threshold_out, int32_t* count_out, void* workspace, size_t workspace_bytes,
+               void* stream);
+
 #ifdef __cplusplus
 }
 #endif

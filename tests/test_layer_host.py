@@ -45,8 +45,7 @@ def test_rewire_changes_only_selected_sources_and_zeroes_moments():
     before_w = layer.kernel_weights.detach().clone()
     version = layer.kernel_indices._version
     opt = Moments(800)
-    gen = torch.Generator().manual_seed(0)
-    locs = layer.rewire(0.1, optimizer=opt, generator=gen)
+    locs = layer.rewire_eager(0.1, optimizer=opt, seed=5)
     assert locs.numel() == 79
     untouched = torch.ones(800, dtype=torch.bool)
     untouched[locs] = False
@@ -56,3 +55,7 @@ def test_rewire_changes_only_selected_sources_and_zeroes_moments():
     assert layer.kernel_indices._version > version                        # cached plans become stale
     assert float(opt.m[0][locs].abs().sum()) == 0 and float(opt.v[0][locs].abs().sum()) == 0
     assert float(opt.m[0][untouched].min()) == 1
+    # the device entry point refuses a layer that lives on the host: there is no CPU path
+    import pytest
+    with pytest.raises(ValueError, match="CUDA"):
+        layer.rewire(0.1)
