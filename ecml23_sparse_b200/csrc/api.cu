@@ -287,8 +287,6 @@ static int backward_impl(const void* x, const int32_t* idx, const void* W, const
     if (gT_in) {
         if (ldg_in < B || ldg_in % 32 != 0 || reinterpret_cast<uintptr_t>(gT_in) % 16 != 0)
             return fail(FFI_ERR_INVALID_ARGUMENT, "gT needs a row stride that is a multiple of 32 and >= B, 16-byte aligned");
-        if (sep_w && !gw_stream)
-            return fail(FFI_ERR_UNSUPPORTED, "this shape needs the untransposed gradient g[B,L] for grad_W");
         if (grad_bias && !fused) {  // the fused backward sums grad_bias from the g tiles it loads
             rc = launch_bias_grad_rows(gT_in, ldg_in, L, grad_bias, stream);
             if (rc != FFI_OK) return rc;
@@ -396,6 +394,8 @@ extern "C" int ffi_backward_from_transposed(const void* x, const int32_t* idx, c
 namespace ffi {
 int launch_forward_bce_stream(const FwdArgs& a, float* gT, int64_t ldg, float scale, double* loss_partials, int* ctas,
                               int loss_kind, cudaStream_t stream, bool* handled);
+int launch_forward_loss_tile(const FwdArgs& a, float* gT, int64_t ldg, float scale, double* loss_partials, int* ctas,
+                             int loss_kind, cudaStream_t stream);
 size_t forward_topk_workspace_bytes(int64_t B);
 int launch_forward_topk_stream(const FwdArgs& a, void* scratch, float* top_val, int* top_idx, int kk, int label_offset,
                                cudaStream_t stream, bool* handled);
@@ -457,9 +457,10 @@ extern "C" int ffi_forward_loss(int loss_kind, const void* x, const int32_t* idx
     bool handled = false;
     rc = launch_forward_bce_stream(a, gT, ldg, scale, partials, &ctas, loss_kind, stream, &handled);
     if (rc != FFI_OK) return rc;
-    if (!handled)
-        return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_loss covers K %% 4 == 0 with x resident in shared memory; "
-                                         "use ffi_forward + ffi_bce_grad for this shape");
+    if (!handled) {  // wide inputs or K % 4 != 0: the CTA-tile kernel with the same epilogue
+        rc = launch_forward_loss_tile(a, gT, ldg, scale, partials, &ctas, loss_kind, stream);
+        if (rc != FFI_OK) return rc;
+    }
     if (static_cast<size_t>(ctas) * sizeof(double) > kBcePartialBytes)
         return fail(FFI_ERR_UNSUPPORTED, "too many loss partials (%d)", ctas);
     return launch_bce_positive_fix(xT, xp.ld, idx, a.W, bias, row_ptr, labels, gT, ldg, loss, partials, ctas,

@@ -35,9 +35,31 @@ struct FwdKernelParams {
     int TO;        // outputs per tile
     int numTiles;  // ceil(L / TO)
     int vec16;     // tiles can be copied with 16-byte cp.async
+    // loss epilogue (LOSS variant): instead of y the kernel writes the loss gradient for target 0, transposed,
+    // gT[o][b] = scale * dloss/dz (zero in the padded batch columns up to ldg), and one partial sum of the
+    // loss values per CTA; the few positives are corrected by a later kernel
+    float* gT;
+    long long ldg;
+    float scale;
+    double* loss_partials;
+    int loss_kind;
 };
 
-template <int BPL, bool XSMEM>
+// loss and d(loss)/dz of one logit whose target is 0 (ffi_loss_kind: BCE, squared hinge, hinge)
+__device__ __forceinline__ void loss_for_negative(int kind, float z, float& value, float& grad) {
+    if (kind == 0) {
+        const float s = __expf(-fabsf(z));
+        const float r = __fdividef(1.f, 1.f + s);
+        value = fmaxf(z, 0.f) + __logf(1.f + s);
+        grad = z >= 0.f ? r : s * r;
+    } else {
+        const float h = fmaxf(1.f + z, 0.f);
+        value = kind == 1 ? h * h : h;
+        grad = kind == 1 ? 2.f * h : (h > 0.f ? 1.f : 0.f);
+    }
+}
+
+template <int BPL, bool XSMEM, bool LOSS>
 __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_kernel(FwdKernelParams p) {
     constexpr int BT = 32 * BPL;
     using V = typename Vec<BPL>::type;
@@ -104,13 +126,34 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_kernel(FwdKernelParams p)
     const size_t ldv = static_cast<size_t>(p.ldx / BPL);
 
     // Coalesced write-out of a finished tile: one warp per batch row, lanes along o.
+    float loss_local = 0.f;
     auto write_out = [&](long long o0, const float* ys) {
-        for (int r = warp; r < BT; r += kWarps) {
-            const int b = b0 + r;
-            if (b >= p.B) break;
-            float* yrow = p.y + static_cast<size_t>(b) * L + o0;
-            for (int c = lane; c < TO; c += 32)
-                if (o0 + c < L) yrow[c] = ys[c * (BT + 1) + r];
+        if constexpr (LOSS) {
+            // one warp per output row, lanes along the batch: gT rows are batch-contiguous
+            const bool last_bt = blockIdx.y + 1 == gridDim.y;
+            const int cols = last_bt ? static_cast<int>(p.ldg) - b0 : BT;  // the last tile also clears the padding
+            for (int c = warp; c < TO; c += kWarps) {
+                if (o0 + c >= L) break;
+                float* grow = p.gT + static_cast<size_t>(o0 + c) * p.ldg + b0;
+                for (int bl = lane; bl < cols; bl += 32) {
+                    float gv = 0.f;
+                    if (bl < BT && b0 + bl < p.B) {
+                        float v, g;
+                        loss_for_negative(p.loss_kind, ys[c * (BT + 1) + bl], v, g);
+                        loss_local += v;
+                        gv = p.scale * g;
+                    }
+                    grow[bl] = gv;
+                }
+            }
+        } else {
+            for (int r = warp; r < BT; r += kWarps) {
+                const int b = b0 + r;
+                if (b >= p.B) break;
+                float* yrow = p.y + static_cast<size_t>(b) * L + o0;
+                for (int c = lane; c < TO; c += 32)
+                    if (o0 + c < L) yrow[c] = ys[c * (BT + 1) + r];
+            }
         }
     };
 
@@ -181,6 +224,20 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_kernel(FwdKernelParams p)
     __pipeline_wait_prior(0);
     __syncthreads();
     if (prev_o0 >= 0) write_out(prev_o0, y_s + (buf ^ 1) * TO * (BT + 1));
+    if constexpr (LOSS) {
+        double v = static_cast<double>(loss_local);
+#pragma unroll
+        for (int off = 16; off >= 1; off /= 2) v += __shfl_xor_sync(0xffffffffu, v, off);
+        __syncthreads();
+        double* red = reinterpret_cast<double*>(smem_raw);
+        if (lane == 0) red[warp] = v;
+        __syncthreads();
+        if (tid == 0) {
+            double t = 0.0;
+            for (int w = 0; w < kWarps; ++w) t += red[w];
+            p.loss_partials[static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x] = t;
+        }
+    }
 }
 
 __global__ void transpose_pad_kernel(const float* __restrict__ src, float* __restrict__ dst,
@@ -222,10 +279,12 @@ int pick_TO(size_t budget, int N, int bpl, bool xsmem, int Kp) {
     return static_cast<int>(to / 16 * 16);
 }
 
-template <int BPL, bool XSMEM>
+constexpr int kMaxLossPartialsTile = 1024;  // doubles the caller's scratch holds for the per-CTA loss sums
+
+template <int BPL, bool XSMEM, bool LOSS>
 int launch_fwd_t(const FwdKernelParams& p, size_t smem, int nBT, const DeviceInfo& dev,
-                 cudaStream_t stream) {
-    auto kern = ffi_fwd_kernel<BPL, XSMEM>;
+                 cudaStream_t stream, int* ctas_out) {
+    auto kern = ffi_fwd_kernel<BPL, XSMEM, LOSS>;
     FFI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(smem)));
     int occ = 0;
@@ -234,9 +293,26 @@ int launch_fwd_t(const FwdKernelParams& p, size_t smem, int nBT, const DeviceInf
     int per_bt = dev.sm_count * occ / nBT;
     if (per_bt < 1) per_bt = 1;
     dim3 grid(static_cast<unsigned>(min(p.numTiles, per_bt)), static_cast<unsigned>(nBT));
+    if (LOSS && static_cast<long long>(grid.x) * grid.y > kMaxLossPartialsTile)
+        return fail(FFI_ERR_UNSUPPORTED, "the fused loss keeps at most %d per-CTA partials; this batch needs %u",
+                    kMaxLossPartialsTile, grid.x * grid.y);
+    if (ctas_out) *ctas_out = static_cast<int>(grid.x * grid.y);
     kern<<<grid, kThreads, smem, stream>>>(p);
     FFI_LAUNCH_CHECK("ffi_fwd_kernel");
     return FFI_OK;
+}
+
+template <bool LOSS>
+int launch_fwd_tile(const FwdKernelParams& p, size_t smem, int nBT, int bpl, bool xsmem, const DeviceInfo& dev,
+                    cudaStream_t stream, int* ctas_out) {
+    if (xsmem) {
+        if (bpl == 4) return launch_fwd_t<4, true, LOSS>(p, smem, nBT, dev, stream, ctas_out);
+        if (bpl == 2) return launch_fwd_t<2, true, LOSS>(p, smem, nBT, dev, stream, ctas_out);
+        return launch_fwd_t<1, true, LOSS>(p, smem, nBT, dev, stream, ctas_out);
+    }
+    if (bpl == 4) return launch_fwd_t<4, false, LOSS>(p, smem, nBT, dev, stream, ctas_out);
+    if (bpl == 2) return launch_fwd_t<2, false, LOSS>(p, smem, nBT, dev, stream, ctas_out);
+    return launch_fwd_t<1, false, LOSS>(p, smem, nBT, dev, stream, ctas_out);
 }
 
 }  // namespace
@@ -260,17 +336,21 @@ bool forward_uses_smem_x(int B, int N, int K, int* bpl_out) {
 
 int launch_forward_stream(const FwdArgs& a, cudaStream_t stream, bool* handled);
 
-int launch_forward(const FwdArgs& a, cudaStream_t stream) {
+// The CTA-tile kernel (any K, unaligned rows, x gathered from L2 when its tile does not fit shared memory);
+// with `loss` set it writes the loss gradient instead of y (see FwdKernelParams).
+struct TileLossEpilogue {
+    float* gT;
+    long long ldg;
+    float scale;
+    double* loss_partials;
+    int loss_kind;
+    int* ctas;
+};
+
+static int launch_forward_tile(const FwdArgs& a, const TileLossEpilogue* loss, cudaStream_t stream) {
     DeviceInfo dev;
     int rc = get_device_info(&dev);
     if (rc != FFI_OK) return rc;
-    {
-        // Preferred: the barrier-free kernel (x tile in shared memory, K % 4 == 0, aligned rows).
-        bool handled = false;
-        rc = launch_forward_stream(a, stream, &handled);
-        if (rc != FFI_OK || handled) return rc;
-    }
-
     FwdKernelParams p;
     p.xT = a.xT;
     p.ldx = a.ldx;
@@ -285,6 +365,11 @@ int launch_forward(const FwdArgs& a, cudaStream_t stream) {
     p.Kp = static_cast<int>(round_up(a.K, 4));
     p.vec16 = (a.K % 4 == 0) && (reinterpret_cast<uintptr_t>(a.W) % 16 == 0) &&
               (reinterpret_cast<uintptr_t>(a.idx) % 16 == 0);
+    p.gT = loss ? loss->gT : nullptr;
+    p.ldg = loss ? loss->ldg : 0;
+    p.scale = loss ? loss->scale : 0.f;
+    p.loss_partials = loss ? loss->loss_partials : nullptr;
+    p.loss_kind = loss ? loss->loss_kind : 0;
 
     int bpl = 1;
     const bool xsmem = forward_uses_smem_x(a.B, a.N, a.K, &bpl);
@@ -299,15 +384,26 @@ int launch_forward(const FwdArgs& a, cudaStream_t stream) {
             reinterpret_cast<uintptr_t>(a.xT) % 16 != 0)
             return fail(FFI_ERR_INVALID_ARGUMENT, "wide-N forward needs a padded, aligned x copy");
     }
+    if (loss) return launch_fwd_tile<true>(p, smem, nBT, bpl, xsmem, dev, stream, loss->ctas);
+    return launch_fwd_tile<false>(p, smem, nBT, bpl, xsmem, dev, stream, nullptr);
+}
 
-    if (xsmem) {
-        if (bpl == 4) return launch_fwd_t<4, true>(p, smem, nBT, dev, stream);
-        if (bpl == 2) return launch_fwd_t<2, true>(p, smem, nBT, dev, stream);
-        return launch_fwd_t<1, true>(p, smem, nBT, dev, stream);
+int launch_forward(const FwdArgs& a, cudaStream_t stream) {
+    {
+        // Preferred: the barrier-free kernel (x tile in shared memory, K % 4 == 0, aligned rows).
+        bool handled = false;
+        int rc = launch_forward_stream(a, stream, &handled);
+        if (rc != FFI_OK || handled) return rc;
     }
-    if (bpl == 4) return launch_fwd_t<4, false>(p, smem, nBT, dev, stream);
-    if (bpl == 2) return launch_fwd_t<2, false>(p, smem, nBT, dev, stream);
-    return launch_fwd_t<1, false>(p, smem, nBT, dev, stream);
+    return launch_forward_tile(a, nullptr, stream);
+}
+
+// Forward with the loss gradient in the epilogue for the shapes the barrier-free kernel does not take
+// (wide inputs, K not a multiple of 4): same outputs as launch_forward_bce_stream.
+int launch_forward_loss_tile(const FwdArgs& a, float* gT, int64_t ldg, float scale, double* loss_partials, int* ctas,
+                             int loss_kind, cudaStream_t stream) {
+    TileLossEpilogue e{gT, ldg, scale, loss_partials, loss_kind, ctas};
+    return launch_forward_tile(a, &e, stream);
 }
 
 int launch_transpose_pad(const float* src, float* dst, int rows, int cols, int64_t ld_dst,

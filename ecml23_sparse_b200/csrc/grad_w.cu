@@ -27,7 +27,9 @@ struct GradWKernelParams {
     const float* xT;
     long long ldx;
     const int* idx;
-    const float* g;
+    const float* g;    // upstream gradient [B][L], or nullptr when gT is given
+    const float* gT;   // upstream gradient transposed to [L][ldg] (batch contiguous, zero padded)
+    long long ldg;
     float* gW;
     float* gbias;
     int B, N, L, K;
@@ -117,15 +119,29 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_grad_w_kernel(GradWKernelPara
 
     // The g tile of the next output tile is fetched into registers while the current tile is
     // being computed (kGRegs * 512 >= TO * BT by construction of TO).
+    // Element e of the tile is (batch row r, output c): consecutive threads run along the contiguous
+    // dimension of whichever layout the gradient comes in.
+    const bool fromT = p.g == nullptr;
+    auto tile_rc = [&](int e, int& r, int& c) {
+        if (fromT) {
+            c = e / BT;
+            r = e - c * BT;
+        } else {
+            r = e / TO;
+            c = e - r * TO;
+        }
+    };
     float gpre[kGRegs];
     auto load_g = [&](int t) {
         const long long o0 = static_cast<long long>(t) * TO;
 #pragma unroll
         for (int u = 0; u < kGRegs; ++u) {
-            const int e = tid + u * kThreads;
-            const int r = e / TO, c = e - r * TO;
+            int r, c;
+            tile_rc(tid + u * kThreads, r, c);
             const int b = b0 + r;
-            gpre[u] = (r < BT && b < p.B && o0 + c < L) ? __ldg(p.g + static_cast<size_t>(b) * L + o0 + c) : 0.f;
+            const bool live = r < BT && c < TO && b < p.B && o0 + c < L;
+            const float* src = fromT ? p.gT + static_cast<size_t>(o0 + c) * p.ldg + b : p.g + static_cast<size_t>(b) * L + o0 + c;
+            gpre[u] = live ? __ldg(src) : 0.f;
         }
     };
 
@@ -141,9 +157,9 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_grad_w_kernel(GradWKernelPara
         // g tile, transposed into g_s[o][b] (row stride BT+1: conflict-free both ways).
 #pragma unroll
         for (int u = 0; u < kGRegs; ++u) {
-            const int e = tid + u * kThreads;
-            const int r = e / TO, c = e - r * TO;
-            if (r < BT) g_s[c * (BT + 1) + r] = gpre[u];
+            int r, c;
+            tile_rc(tid + u * kThreads, r, c);
+            if (r < BT && c < TO) g_s[c * (BT + 1) + r] = gpre[u];
         }
         __pipeline_wait_prior(0);
         __syncthreads();  // idx tile t and g_s visible
@@ -315,6 +331,9 @@ int launch_grad_w(const GradWArgs& a, cudaStream_t stream) {
     p.ldx = a.ldx;
     p.idx = a.idx;
     p.g = a.g;
+    p.gT = a.gT;
+    p.ldg = a.ldg;
+    if (!a.g && !a.gT) return fail(FFI_ERR_INVALID_ARGUMENT, "grad_W needs the upstream gradient");
     p.gW = a.gW;
     p.gbias = a.gbias;
     p.B = a.B;

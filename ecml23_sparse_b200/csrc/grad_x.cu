@@ -44,13 +44,15 @@ struct GxNarrowParams {
     long long ldg;
     const int* cperm;
     const int* cptr;
-    float* partial;  // [R][N][Bpad]
+    float* partial;  // [R * S][N][Bpad]
     int B, N, L, K;
     int T;           // rows per chunk
     long long nChunks;
     int R;           // number of chunk ranges (gridDim.x)
     int Bpad;
     int entCap;      // capacity of the staged entry buffer (entries)
+    int segChunks;   // chunks per flushed partial: the running fp32 sums restart after that many chunks
+    int S;           // partial slots per range
 };
 
 template <int NI, int BPL>
@@ -173,17 +175,38 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_grad_x_narrow_kernel(GxNarrow
         if (e_hi == e_lo) {
             __pipeline_wait_prior(0);
         }
+        // Every segChunks chunks the running sums go out as one partial (partial[r*S + seg][i][b]) and
+        // restart from zero, so that no fp32 sum runs over more than a few hundred products; the
+        // partials are added in fp64 afterwards.
+        const long long done = c - c_begin + 1;
+        if (done % p.segChunks == 0 || c + 1 == c_end) {
+            const int seg = static_cast<int>((done - 1) / p.segChunks);
+#pragma unroll
+            for (int j = 0; j < NI; ++j) {
+                const int i = i_lo + warp * NI + j;
+                if (i < N) {
+                    float* dst = p.partial + ((static_cast<size_t>(r) * p.S + seg) * N + i) * p.Bpad + b0 + lane * BPL;
+#pragma unroll
+                    for (int q = 0; q < BPL; ++q) {
+                        dst[q] = acc[j][q];
+                        acc[j][q] = 0.f;
+                    }
+                }
+            }
+        }
     }
     __pipeline_wait_prior(0);
 
-    // Range partials: partial[r][i][b0 + lane*BPL + q].
+    // Segments a range never reached hold zeros (ranges differ by at most one chunk).
+    for (int seg = static_cast<int>((c_end - c_begin + p.segChunks - 1) / p.segChunks); seg < p.S; ++seg) {
 #pragma unroll
-    for (int j = 0; j < NI; ++j) {
-        const int i = i_lo + warp * NI + j;
-        if (i < N) {
-            float* dst = p.partial + (static_cast<size_t>(r) * N + i) * p.Bpad + b0 + lane * BPL;
+        for (int j = 0; j < NI; ++j) {
+            const int i = i_lo + warp * NI + j;
+            if (i < N) {
+                float* dst = p.partial + ((static_cast<size_t>(r) * p.S + seg) * N + i) * p.Bpad + b0 + lane * BPL;
 #pragma unroll
-            for (int q = 0; q < BPL; ++q) dst[q] = acc[j][q];
+                for (int q = 0; q < BPL; ++q) dst[q] = 0.f;
+            }
         }
     }
 }
@@ -268,11 +291,14 @@ int launch_narrow_t(const GxNarrowParams& p, size_t smem, int iparts, int nBT, c
 }
 
 struct NarrowConfig {
-    int bpl, ni, iparts, nBT, Bpad, R, entCap;
+    int bpl, ni, iparts, nBT, Bpad, R, entCap, segChunks, S;
     size_t smem;
 };
 
-bool narrow_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, NarrowConfig* c) {
+// max_partial_bytes bounds the scratch for the range partials (R * S slots of N * Bpad floats): the segments
+// get longer when the scratch is small (S = 1: one partial per range).
+bool narrow_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, NarrowConfig* c,
+                   size_t max_partial_bytes = static_cast<size_t>(256) << 20) {
     if (!plan->has_chunks) return false;
     c->bpl = B <= 32 ? 1 : (B <= 64 ? 2 : 4);
     c->ni = 64 / c->bpl;  // 64 accumulator registers per lane
@@ -294,6 +320,22 @@ bool narrow_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, Narro
     if (cap < 64) return false;
     c->entCap = static_cast<int>(cap);
     c->smem = gbytes + cap * 8 + cpbytes;
+    // flush after about 256 summands per (input, batch) pair, as far as the scratch allows
+    const double per_chunk = static_cast<double>(plan->chunk_rows) * plan->K / static_cast<double>(plan->N);
+    long long seg = static_cast<long long>(256.0 / (per_chunk > 1.0 ? per_chunk : 1.0));
+    if (seg < 1) seg = 1;
+    const long long perRange = ceil_div(plan->n_chunks, R);
+    const size_t slot = static_cast<size_t>(plan->N) * c->Bpad * 4;
+    long long maxS = static_cast<long long>(max_partial_bytes / (slot * R));
+    if (maxS < 1) maxS = 1;
+    long long S = ceil_div(perRange, seg);
+    if (S > maxS) {
+        S = maxS;
+        seg = ceil_div(perRange, S);
+        S = ceil_div(perRange, seg);
+    }
+    c->segChunks = static_cast<int>(seg);
+    c->S = static_cast<int>(S);
     return true;
 }
 
@@ -367,7 +409,16 @@ size_t grad_x_workspace_bytes(const ffi_plan* plan, int64_t B) {
     DeviceInfo dev;
     if (get_device_info(&dev) != FFI_OK) return 0;
     NarrowConfig c;
-    if (narrow_config(plan, B, dev, &c)) return static_cast<size_t>(c.R) * plan->N * c.Bpad * 4;
+    if (narrow_config(plan, B, dev, &c)) return static_cast<size_t>(c.R) * c.S * plan->N * c.Bpad * 4;
+    return 0;
+}
+
+// The least scratch the narrow kernel can run with: one partial per range.
+size_t grad_x_min_workspace_bytes(const ffi_plan* plan, int64_t B) {
+    DeviceInfo dev;
+    if (get_device_info(&dev) != FFI_OK) return 0;
+    NarrowConfig c;
+    if (narrow_config(plan, B, dev, &c, 1)) return static_cast<size_t>(c.R) * plan->N * c.Bpad * 4;
     return 0;
 }
 
@@ -380,8 +431,10 @@ int launch_grad_x(const GradXArgs& a, cudaStream_t stream) {
         return fail(FFI_ERR_INVALID_ARGUMENT, "grad_x needs the transposed upstream gradient");
 
     NarrowConfig c;
-    if (narrow_config(plan, a.B, dev, &c)) {
-        const size_t need = grad_x_workspace_bytes(plan, a.B);
+    // a caller with little scratch (the allocation-free entry point) gets longer segments
+    if (narrow_config(plan, a.B, dev, &c, a.workspace_bytes < (static_cast<size_t>(256) << 20) ? a.workspace_bytes
+                                                                                                : (static_cast<size_t>(256) << 20))) {
+        const size_t need = static_cast<size_t>(c.R) * c.S * plan->N * c.Bpad * 4;
         if (!a.workspace || a.workspace_bytes < need)
             return fail(FFI_ERR_WORKSPACE, "grad_x needs %zu bytes of workspace, got %zu", need, a.workspace_bytes);
         if (reinterpret_cast<uintptr_t>(a.workspace) % 16 != 0)
@@ -403,13 +456,15 @@ int launch_grad_x(const GradXArgs& a, cudaStream_t stream) {
         p.R = c.R;
         p.Bpad = c.Bpad;
         p.entCap = c.entCap;
+        p.segChunks = c.segChunks;
+        p.S = c.S;
         if (c.bpl == 4) rc = launch_narrow_t<16, 4>(p, c.smem, c.iparts, c.nBT, stream);
         else if (c.bpl == 2) rc = launch_narrow_t<32, 2>(p, c.smem, c.iparts, c.nBT, stream);
         else rc = launch_narrow_t<64, 1>(p, c.smem, c.iparts, c.nBT, stream);
         if (rc != FFI_OK) return rc;
         const long long total = static_cast<long long>(a.N) * c.Bpad;
         reduce_partials_kernel<<<static_cast<unsigned>(ceil_div(total, 256)), 256, 0, stream>>>(
-            p.partial, a.gx, c.R, a.N, a.B, c.Bpad, a.x_transposed);
+            p.partial, a.gx, c.R * c.S, a.N, a.B, c.Bpad, a.x_transposed);
         FFI_LAUNCH_CHECK("reduce_partials_kernel");
         return FFI_OK;
     }
@@ -489,7 +544,7 @@ extern "C" int ffi_grad_x_static(const float* W, const float* gT, int64_t ldg, c
         return fail(FFI_ERR_INVALID_ARGUMENT,
                     "gT must be 16-byte aligned with a row stride that is a multiple of 32 and >= "
                     "ffi_transposed_gradient_stride(B) = %lld", (long long)transposed_g_stride(B));
-    const size_t need = grad_x_workspace_bytes(plan, B);
+    const size_t need = grad_x_min_workspace_bytes(plan, B);
     if (need > kStaticScratchBytes)
         return fail(FFI_ERR_WORKSPACE,
                     "ffi_grad_x_static: this shape needs %zu bytes of scratch, the built-in array holds %zu; "

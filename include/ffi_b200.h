@@ -136,8 +136,7 @@ int ffi_transpose_gradient(const float* g, float* gT, float* grad_bias, int64_t 
 /*
  * ffi_backward for a caller that already holds the transposed gradient gT[L][ldg] (from
  * ffi_forward_bce or ffi_transpose_gradient): no transposition pass.  grad_bias, when requested,
- * is the row sum of gT.  Returns FFI_ERR_UNSUPPORTED for the few shapes whose grad_W kernel
- * needs g[B,L] itself (K not a multiple of 4 together with a batch above 128 or wide N).
+ * is the row sum of gT.  Every shape ffi_backward takes is covered.
  */
 int ffi_backward_from_transposed(const void* x, const int32_t* idx, const void* W, const float* gT,
                                  int64_t ldg, const ffi_plan* plan, float* grad_x, float* grad_w,
@@ -154,9 +153,8 @@ int ffi_backward_from_transposed(const void* x, const int32_t* idx, const void* 
  * one row distinct; L_total / label_offset describe a label shard).  Replaces the chain
  * FanInSparseMatmulTp -> bias_add -> SparseBinaryCrossEntropyLoss -> its gradient
  * (sparse/custom_layer.py:45-50, sparse/layer.py:245-247, sparse/metrics.py:132-139,167-173).
- * Covers K % 4 == 0 with the x tile resident in shared memory; other shapes return
- * FFI_ERR_UNSUPPORTED (use ffi_forward + ffi_bce_grad).  Workspace: 256-byte aligned,
- * ffi_forward_bce_workspace_bytes bytes.
+ * Every shape ffi_forward takes is covered (wide inputs and K % 4 != 0 run the tiled forward kernel
+ * with the same epilogue).  Workspace: 256-byte aligned, ffi_forward_bce_workspace_bytes bytes.
  */
 size_t ffi_forward_bce_workspace_bytes(int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed,
                                        int dtype);
@@ -226,7 +224,8 @@ int ffi_grad_x_static(const float* W, const float* gT, int64_t ldg, const ffi_pl
  * tf.nn.top_k (value descending, lower index first on ties).  It is what PrecisionAtK
  * (sparse/metrics.py:9-70: topk_as_matrix + the overlap with the true labels) needs from the
  * B x L logits, which here never reach HBM; with a sharded label dimension every shard returns
- * its own k candidates.  Same shape coverage as ffi_forward_loss (FFI_ERR_UNSUPPORTED otherwise).
+ * its own k candidates.  Covers K % 4 == 0 with the x tile resident in shared memory
+ * (FFI_ERR_UNSUPPORTED otherwise: use ffi_forward and a top-k over y there).
  */
 size_t ffi_forward_topk_workspace_bytes(int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed,
                                         int dtype);

@@ -37,14 +37,16 @@ RTOL = 1e-5
 ATOL = 1e-5
 
 
-def gx_atol(L, K, N):
-    """Absolute floor for grad_x.  grad_x[b,i] sums n = L*K/N products; the rounding error of any
-    fp32 summation grows like sqrt(n) times the size of the partial sums, independently of how
-    close to zero the total lands, so the 1e-5 floor (meant for O(1) sums) is widened by
-    sqrt(n)/32 once n exceeds 1024.  The reference's own fp32 running sum is further from the fp64
-    value than this (checked on the 4,000,000-unit fixture in test_gpu_parity.py)."""
+def gx_atol(L, K, N, term_rms=0.25):
+    """Absolute floor for grad_x.  grad_x[b,i] sums n = L*K/N products W*g; the rounding error of any
+    fp32 summation grows like sqrt(n) times the size of the summands, independently of how close to
+    zero the total lands, so the 1e-5 floor (meant for O(1) sums of a few terms) is widened by
+    sqrt(n)/32 once n exceeds 1024, and in proportion to the summands' scale where that exceeds the
+    0.25 of the benchmark's distributions (W ~ N(0, 1/K) with K >= 16, g ~ N(0,1)).  The reference's
+    own fp32 running sum is further from the fp64 value than this (checked on the 4,000,000-unit
+    fixture in test_gpu_parity.py)."""
     n = L * K / N
-    return ATOL * max(1.0, n ** 0.5 / 32.0)
+    return ATOL * max(1.0, n ** 0.5 / 32.0) * max(1.0, term_rms / 0.25)
 
 
 def size_id(size) -> str:

@@ -146,9 +146,9 @@ def test_wide_output_layers_of_configs_1_to_4(cuda_device, shape):
 
 def test_offsets_beyond_two_to_the_31(cuda_device):
     """B*L >= 2^31 elements in y and g (the reference indexes batch*L+unit in int32,
-    tfsparse/cc/kernels/kernel_data.cu.h:221-225): B=1024, N=32, L=2,100,000, K=4."""
+    tfsparse/cc/kernels/kernel_data.cu.h:221-225): B=1024, N=512, L=2,100,000, K=4."""
     dev = cuda_device
-    B, N, L, K = 1024, 32, 2_100_000, 4
+    B, N, L, K = 1024, 512, 2_100_000, 4
     assert B * L >= 2 ** 31
     xT, idx, W, _ = make_inputs(dev, B, N, 1, K, seed=400)
     idx = synth.indices_without_replacement(400, 1, L, K, N, device=dev)
@@ -166,7 +166,7 @@ def test_offsets_beyond_two_to_the_31(cuda_device):
         worst_w = max(worst_w, excess(gW[o0:o1], gW_ref, ATOL * 4))  # sums of 1024 products
         worst_b = max(worst_b, excess(gb[o0:o1], g[:, o0:o1].double().sum(0), bias_atol(B)))
     assert worst_y <= 0 and worst_w <= 0 and worst_b <= 0, (worst_y, worst_w, worst_b)
-    ex = excess(gx, holder.gx, gx_atol(L, K, N))
+    ex = excess(gx, holder.gx, gx_atol(L, K, N, term_rms=0.5))  # W ~ N(0, 1/K) with K = 4: summands of scale 0.5
     assert ex <= 0, f"grad_x exceeds the tolerance by {ex:.3e}"
     # the last rows and the last batch element live beyond the 2^31-th element
     rows = np.r_[L - 32:L]

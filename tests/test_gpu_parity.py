@@ -408,7 +408,9 @@ def test_headline_shape_full_size(cuda_device):
 def test_transpose_gradient_and_backward_from_transposed(cuda_device):
     dev = cuda_device
     from ecml23_sparse_b200 import ops
-    for shape in [(128, 768, 5_001, 32), (37, 254, 513, 16), (200, 100, 300, 8)]:
+    # the last three take the tiled grad_W kernel (wide inputs, K not a multiple of 4), which reads either layout
+    for shape in [(128, 768, 5_001, 32), (37, 254, 513, 16), (200, 100, 300, 8), (130, 3_000, 1_000, 16),
+                  (70, 300, 500, 7), (128, 32_768, 2_001, 32)]:
         B, N, L, K = shape
         x, idx, W, g = reference_style_inputs(shape, seed=3, relu_grad=False)
         gT, gb = ops.transpose_gradient(to_cuda(g, dev), want_bias_grad=True)
@@ -531,14 +533,31 @@ def test_fused_forward_topk_and_precision_at_k(cuda_device, shape, transposed):
         assert abs(got - want) <= (1.0 - decided.mean()) + 1e-12
 
 
-def test_fused_forward_bce_reports_unsupported_shapes(cuda_device):
+@pytest.mark.parametrize("shape", [(17, 64, 63, 45), (70, 300, 500, 7), (130, 3_000, 1_000, 16), (128, 32_768, 3_001, 32)],
+                         ids=["K45", "K7_B70", "wide_N3000_B130", "wide_N32768"])
+@pytest.mark.parametrize("loss_name", ["bce", "squared_hinge"])
+def test_fused_forward_loss_on_tiled_kernel_shapes(cuda_device, shape, loss_name):
+    """Shapes the barrier-free forward does not take (K not a multiple of 4, x too wide for shared memory):
+    the tiled forward kernel carries the same loss epilogue."""
     dev = cuda_device
     from ecml23_sparse_b200 import ops
-    x, idx, W, _ = reference_style_inputs((17, 12, 63, 44 + 1))  # K = 45 is not a multiple of 4
-    row_ptr, labels = synth.multi_hot_targets(1, 2, 17, 63)
-    with pytest.raises(_lib.FFIError) as e:
-        ops.forward_bce(to_cuda(x, dev), to_cuda(idx, dev), to_cuda(W, dev), None, row_ptr, labels, False)
-    assert e.value.status == 2
+    B, N, L, K = shape
+    x, idx, W, _ = config_style_inputs(B, N, L, K, seed=19)
+    W = W * 4
+    bias = synth.normal(19, 40, (L,), std=0.5).numpy()
+    row_ptr, labels = synth.multi_hot_targets(19, 41, B, L)
+    loss, gT = ops.forward_bce(to_cuda(x, dev), to_cuda(idx, dev), to_cuda(W, dev), to_cuda(bias, dev), row_ptr, labels,
+                               False, loss=loss_name)
+    z = oracle.forward_f64(x, idx, W, bias=bias).astype(np.float32)
+    if loss_name == "bce":
+        loss_ref, g_ref = oracle.bce_f64(z, row_ptr.numpy(), labels.numpy())
+        # positives with a large logit: sigmoid(z) - 1 cancels, so the floor is relative to the scale 1/(B*L)
+        assert_close(gT[:, :B].t().cpu().numpy(), g_ref, 5e-5, 2e-7 / (B * L), "fused BCE gradient (tiled kernel)")
+    else:
+        loss_ref, g_ref = oracle.hinge_f64(z, row_ptr.numpy(), labels.numpy(), squared=True)
+        assert np.abs(gT[:, :B].t().cpu().numpy() - g_ref).max() <= 4e-5 / (B * L) * max(1.0, np.abs(z).max())
+    assert abs(float(loss) - loss_ref) <= 2e-5 * abs(loss_ref) + 1e-7
+    assert gT.shape[1] >= B and not gT[:, B:].any()
 
 
 @pytest.mark.parametrize("shape,transposed", [((64, 512, 3_001, 32), True), ((37, 254, 513, 16), False),
