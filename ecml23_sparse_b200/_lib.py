@@ -31,7 +31,7 @@ FFI_LOSS_HINGE = 2
 EXPORTED_SYMBOLS = (
     "ffi_last_error", "ffi_version",
     "ffi_forward_workspace_bytes", "ffi_forward",
-    "ffi_plan_create", "ffi_plan_destroy", "ffi_plan_info", "ffi_plan_export", "ffi_plan_export_chunked",
+    "ffi_plan_create", "ffi_plan_rebuild", "ffi_plan_destroy", "ffi_plan_info", "ffi_plan_export", "ffi_plan_export_chunked",
     "ffi_backward_workspace_bytes", "ffi_backward",
     "ffi_grad_x_static_max_scratch_bytes", "ffi_grad_x_static",
     "ffi_transposed_gradient_stride", "ffi_transpose_gradient",
@@ -65,6 +65,8 @@ def _declare(lib):
     lib.ffi_forward.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp, sz, vp]
     lib.ffi_plan_create.restype = i32
     lib.ffi_plan_create.argtypes = [vp, i64, i64, i64, vp, ctypes.POINTER(vp)]
+    lib.ffi_plan_rebuild.restype = i32
+    lib.ffi_plan_rebuild.argtypes = [vp, vp, vp]
     lib.ffi_plan_destroy.restype = i32
     lib.ffi_plan_destroy.argtypes = [vp]
     lib.ffi_plan_info.restype = i32

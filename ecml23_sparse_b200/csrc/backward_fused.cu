@@ -457,10 +457,11 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsig
 struct Lane8 {
     u64 a, b, c, d;
     __device__ __forceinline__ void zero() { a = b = c = d = 0ull; }
-    // columns 4q..4q+3 at ptr, columns 64+4q..64+4q+3 256 bytes further
+    // columns 4q..4q+3 at ptr, columns BT/2+4q..BT/2+4q+3 HALF bytes further (HALF = 2*BT: half a tile row)
+    template <int HALF>
     __device__ __forceinline__ void load_shared(const unsigned char* ptr) {
         const ulonglong2 t0 = *reinterpret_cast<const ulonglong2*>(ptr);
-        const ulonglong2 t1 = *reinterpret_cast<const ulonglong2*>(ptr + 256);
+        const ulonglong2 t1 = *reinterpret_cast<const ulonglong2*>(ptr + HALF);
         a = t0.x, b = t0.y, c = t1.x, d = t1.y;
     }
     __device__ __forceinline__ void axpy(float w, const Lane8& g) {
@@ -505,18 +506,26 @@ __device__ __forceinline__ void tmem_store_sums(unsigned taddr, const Lane8& sum
         : "memory");
 }
 
-template <int NI, int THREADS, int SLOTS>
+// G lane groups per warp: a group of 32/G lanes covers the BT = 256/G batch columns of one entry (8 per lane),
+// so a warp step works on G consecutive entries of a run.  G = 2 is the batch 65..128 case described above;
+// G = 4 covers batch <= 64 with a quarter of a warp per entry (a quarter warp reads one 128-byte half of a
+// tile row per LDS.128: conflict-free), which halves the shared-memory traffic per entry once more.
+template <int NI, int THREADS, int SLOTS, int G>
 __global__ void __launch_bounds__(THREADS, 1)
     ffi_bwd_pairs_kernel(BwdFusedParams p, const __grid_constant__ CUtensorMap g_map) {
-    constexpr int BT = 128;
+    constexpr int LG = 32 / G;    // lanes per group
+    constexpr int BT = 8 * LG;    // batch columns of the tile
+    constexpr int HALF = 2 * BT;  // bytes between a lane's two 16-byte pieces of a tile row
     constexpr int kThreads = THREADS, kWarps = THREADS / 32, kSlots = SLOTS;  // shadow the file-wide values
     constexpr int CPN = kWarps * NI + 1;
     constexpr unsigned kRowMask = (1u << kKShift) - 1u;
     static_assert((THREADS / 128) * NI * 16 <= kTmemCols, "the warps of a lane quarter share the TMEM columns");
+    static_assert(SLOTS * G == 32, "the lane reduction maps the 32 lanes to (buffered step, group)");
+    static_assert(32 + G <= kDRow, "a dot-buffer row holds 32 dots and G entry codes");
     extern __shared__ __align__(1024) unsigned char smem_raw[];
 
     const int T = p.T, K = p.K, N = p.N;
-    float* g_s = reinterpret_cast<float*>(smem_raw);                                    // [T][128], row-major
+    float* g_s = reinterpret_cast<float*>(smem_raw);                                    // [T][BT], row-major
     uint2* ent_s = reinterpret_cast<uint2*>(g_s + static_cast<size_t>(T) * BT);         // [2][entCap]
     float* dbuf_s = reinterpret_cast<float*>(ent_s + 2 * p.entCap);                     // [warps][kSlots][kDRow]
     int* cp_s = reinterpret_cast<int*>(dbuf_s + kWarps * kSlots * kDRow);               // [2][CPN]
@@ -526,8 +535,8 @@ __global__ void __launch_bounds__(THREADS, 1)
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
-    const int half = lane >> 4;  // which entry of a pair this lane works on
-    const int q = lane & 15;
+    const int grp = lane / LG;  // which entry of a step this lane works on
+    const int q = lane % LG;
     const int r = blockIdx.x;
     const int i_lo = blockIdx.y * (kWarps * NI);
     const int i_hi = min(N, i_lo + kWarps * NI);
@@ -543,14 +552,13 @@ __global__ void __launch_bounds__(THREADS, 1)
     // lanes 32*(warp % 4) .. +31 are the ones this warp may touch; its inputs take NI*16 columns
     const unsigned taddr0 = tmem_base + ((static_cast<unsigned>(warp & 3) * 32u) << 16) +
                             static_cast<unsigned>(warp >> 2) * (NI * 16);
-    static_assert(SLOTS == 16 || SLOTS == 8, "the lane reduction maps lanes to (row, half)");
 
     for (int j = 0; j < NI; ++j) {
         const int i = i_lo + warp * NI + j;
         unsigned xv[8], zero[8];
 #pragma unroll
         for (int m = 0; m < 8; ++m) {
-            const int b = (m < 4 ? 0 : 64) + 4 * q + (m & 3);
+            const int b = (m < 4 ? 0 : BT / 2) + 4 * q + (m & 3);
             xv[m] = __float_as_uint((i < N && b < p.B) ? __ldg(p.xT + static_cast<size_t>(i) * p.ldx + b) : 0.f);
             zero[m] = 0u;
         }
@@ -615,15 +623,16 @@ __global__ void __launch_bounds__(THREADS, 1)
     __pipeline_wait_prior(0);
     float* dbuf = dbuf_s + warp * (kSlots * kDRow);
     float* dlane = dbuf + lane;                                   // this lane's column of the dot buffer
-    const int dcode_delta = 32 + half - lane;                     // from a lane's dot to its entry's code
+    const int dcode_delta = 32 + grp - lane;                      // from a lane's dot to its entry's code
     const float* dlast1 = dlane + (kSlots - 1) * kDRow;           // last row a single step may fill
     const float* dlast2 = dlane + (kSlots - 2) * kDRow;           // last row a double step may start at
-    const int myrow = min(lane >> 1, kSlots - 1);  // lanes past 2*kSlots idle in the reduction
-    const float4* drow = reinterpret_cast<const float4*>(dbuf + myrow * kDRow + (lane & 1) * 16);
-    const unsigned* dmine = reinterpret_cast<const unsigned*>(dbuf) + myrow * kDRow + 32 + (lane & 1);
+    const int myrow = lane / G, myent = lane % G;                 // the (buffered step, entry) this lane reduces
+    const float4* drow = reinterpret_cast<const float4*>(dbuf + myrow * kDRow + myent * LG);
+    const unsigned* dmine = reinterpret_cast<const unsigned*>(dbuf) + myrow * kDRow + 32 + myent;
     const unsigned char* gs_lane = reinterpret_cast<const unsigned char*>(g_s) + q * 16;
     const unsigned tileBytes = static_cast<unsigned>(T) * (BT * 4);
     bool gave_up = false;
+    long long pending = -1;  // chunk whose tile copy has been issued and not yet seen complete
 
     long long c = c_begin;
     for (; c < c_end; ++c) {
@@ -635,7 +644,8 @@ __global__ void __launch_bounds__(THREADS, 1)
             break;
         }
 
-        // The g tile of the chunk: one TMA box [T rows][128 columns] of gT (rows past L arrive as zeros).
+        // The g tile of the chunk: one TMA box [T rows][BT columns] of gT (rows past L and columns past the
+        // stored row arrive as zeros).
         // (A second tile buffer filled one chunk ahead was measured: it needs T <= 168 to fit, and the
         // shorter runs cost more than the hidden copy saves.)
         if (tid == 0) {
@@ -643,6 +653,7 @@ __global__ void __launch_bounds__(THREADS, 1)
             mbar_expect_tx(g_bar, tileBytes);
             tma_load_2d(g_s, &g_map, 0, static_cast<int>(o0), g_bar);
         }
+        pending = c;
         if (c + 1 < c_end) emit(c + 1, buf ^ 1, pl_lo, pl_cnt);
         __pipeline_commit();
         if (c + 2 < c_end) {
@@ -652,42 +663,50 @@ __global__ void __launch_bounds__(THREADS, 1)
         if (c + 3 < c_end) slice_bounds(c + 3, nb_lo, nb_cnt);
         // Each thread waits for the tile itself; one that gives up says so at the next barrier (the
         // walk of this chunk then reads a stale tile, which is harmless: the result is void anyway).
-        if (!mbar_wait_bounded(g_bar, static_cast<unsigned>(c - c_begin) & 1u)) {
+        if (mbar_wait_bounded(g_bar, static_cast<unsigned>(c - c_begin) & 1u)) {
+            pending = -1;
+        } else {
             atomicAdd(&g_wait_timeouts, 1);
             gave_up = true;
         }
 
-        // grad_bias of the chunk's rows: the slices of a range take turns, each row is a half warp's sum
+        // grad_bias of the chunk's rows: the slices of a range take turns, each row is one group's sum
         if (p.gbias && static_cast<int>(c % gridDim.y) == static_cast<int>(blockIdx.y)) {
-            for (int rr = 2 * warp + half; rr < T; rr += 2 * kWarps) {
+            for (int rr = G * warp + grp; rr < T; rr += G * kWarps) {
                 Lane8 v;
-                v.load_shared(gs_lane + rr * (BT * 4));
+                v.load_shared<HALF>(gs_lane + rr * (BT * 4));
                 float sum = v.sum();
 #pragma unroll
-                for (int off = 8; off >= 1; off /= 2) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                for (int off = LG / 2; off >= 1; off /= 2) sum += __shfl_xor_sync(0xffffffffu, sum, off);
                 if (q == 0 && o0 + rr < p.L) p.gbias[o0 + rr] = sum;
             }
         }
 
-        // ---- walk the runs of this warp's inputs, two entries per step ------------------------
-        const uint2* ent = ent_s + buf * p.entCap + half;  // this half's entry of a step
+        // ---- walk the runs of this warp's inputs, G entries per step ---------------------------
+        const uint2* ent = ent_s + buf * p.entCap + grp;  // this group's entry of a step
         const int* cp = cp_s + buf * CPN + warp * NI;
         float* gWc = p.gW ? p.gW + static_cast<size_t>(o0) * K : nullptr;
-        // Row of the dot buffer the next step fills: 32 per-lane dots, then the codes of its two entries.
+        // Row of the dot buffer the next step fills: 32 per-lane dots, then the codes of its G entries.
         // dptr points at this lane's column of that row; the code of the lane's entry goes to
-        // dptr + dcode_delta (written by every lane of the half: same address, same value).
+        // dptr + dcode_delta (written by every lane of the group: same address, same value).
         float* dptr = dlane;
 
-        // Lane 2*row + h adds the 16 dots of half h of buffered step `row` (fixed order) and stores
+        // Lane row*G + h adds the 32/G dots of entry h of buffered step `row` (fixed order) and stores
         // grad_W of that entry.
         auto reduce_slots = [&]() {
             __syncwarp();
             const int rows = static_cast<int>(dptr - dlane) / kDRow;
-            const float4 q0 = drow[0], q1 = drow[1], q2 = drow[2], q3 = drow[3];
+            float sum;
+            if constexpr (LG == 16) {
+                const float4 q0 = drow[0], q1 = drow[1], q2 = drow[2], q3 = drow[3];
+                sum = (((q0.x + q0.y) + (q0.z + q0.w)) + ((q1.x + q1.y) + (q1.z + q1.w))) +
+                      (((q2.x + q2.y) + (q2.z + q2.w)) + ((q3.x + q3.y) + (q3.z + q3.w)));
+            } else {
+                const float4 q0 = drow[0], q1 = drow[1];
+                sum = ((q0.x + q0.y) + (q0.z + q0.w)) + ((q1.x + q1.y) + (q1.z + q1.w));
+            }
             const unsigned code = *dmine;
-            const float sum = (((q0.x + q0.y) + (q0.z + q0.w)) + ((q1.x + q1.y) + (q1.z + q1.w))) +
-                              (((q2.x + q2.y) + (q2.z + q2.w)) + ((q3.x + q3.y) + (q3.z + q3.w)));
-            if ((lane >> 1) < rows && lane < 2 * kSlots && code != kPadCode && gWc) gWc[code >> kKShift] = sum;
+            if (myrow < rows && code != kPadCode && gWc) gWc[code >> kKShift] = sum;
             __syncwarp();
             dptr = dlane;
         };
@@ -699,12 +718,12 @@ __global__ void __launch_bounds__(THREADS, 1)
             if (e >= t) continue;
             Lane8 acc, xr;
             tmem_load_input(taddr0 + j * 16, acc, xr);
-            // two steps (four entries) per iteration: all loads are issued before the stores
-            for (; e + 4 <= t; e += 4) {
-                const uint2 en0 = ent[e], en1 = ent[e + 2];
+            // two steps (2 G entries) per iteration: all loads are issued before the stores
+            for (; e + 2 * G <= t; e += 2 * G) {
+                const uint2 en0 = ent[e], en1 = ent[e + G];
                 Lane8 g0, g1;
-                g0.load_shared(gs_lane + (en0.y & kRowMask));
-                g1.load_shared(gs_lane + (en1.y & kRowMask));
+                g0.load_shared<HALF>(gs_lane + (en0.y & kRowMask));
+                g1.load_shared<HALF>(gs_lane + (en1.y & kRowMask));
                 if (dptr > dlast2) reduce_slots();
                 acc.axpy(__uint_as_float(en0.x), g0);
                 acc.axpy(__uint_as_float(en1.x), g1);
@@ -714,24 +733,24 @@ __global__ void __launch_bounds__(THREADS, 1)
                 reinterpret_cast<unsigned*>(dptr + dcode_delta)[kDRow] = en1.y;
                 dptr += 2 * kDRow;
             }
-            if (e + 2 <= t) {
+            if (e + G <= t) {
                 const uint2 en0 = ent[e];
                 Lane8 g0;
-                g0.load_shared(gs_lane + (en0.y & kRowMask));
+                g0.load_shared<HALF>(gs_lane + (en0.y & kRowMask));
                 if (dptr > dlast1) reduce_slots();
                 acc.axpy(__uint_as_float(en0.x), g0);
                 dptr[0] = xr.dot(g0);
                 reinterpret_cast<unsigned*>(dptr + dcode_delta)[0] = en0.y;
                 dptr += kDRow;
-                e += 2;
+                e += G;
             }
-            if (e < t) {  // odd run: the last step has an entry for half 0 only
+            if (e < t) {  // the run's last step has entries for the first t - e groups only
                 uint2 en0 = make_uint2(0u, kPadCode);
                 Lane8 g0;
                 g0.zero();
-                if (half == 0) {
+                if (grp < t - e) {
                     en0 = ent[e];
-                    g0.load_shared(gs_lane + (en0.y & kRowMask));
+                    g0.load_shared<HALF>(gs_lane + (en0.y & kRowMask));
                 }
                 if (dptr > dlast1) reduce_slots();
                 acc.axpy(__uint_as_float(en0.x), g0);
@@ -763,12 +782,13 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
                 for (int m = 0; m < 8; ++m) {
                     out[m] = __uint_as_float(av[m]);
-                    out[m] += __shfl_xor_sync(0xffffffffu, out[m], 16);  // the two halves
+#pragma unroll
+                    for (int off = 16; off >= LG; off /= 2) out[m] += __shfl_xor_sync(0xffffffffu, out[m], off);  // the groups
                 }
-                if (i < N && half == 0) {
+                if (i < N && grp == 0) {
                     float* dst = p.partial + ((static_cast<size_t>(r) * p.S + seg) * N + i) * p.Bpad + 4 * q;
                     *reinterpret_cast<float4*>(dst) = make_float4(out[0], out[1], out[2], out[3]);
-                    *reinterpret_cast<float4*>(dst + 64) = make_float4(out[4], out[5], out[6], out[7]);
+                    *reinterpret_cast<float4*>(dst + BT / 2) = make_float4(out[4], out[5], out[6], out[7]);
                 }
             }
             tmem_wait_store();
@@ -779,16 +799,17 @@ __global__ void __launch_bounds__(THREADS, 1)
     for (int seg = static_cast<int>((c_end - c_begin + p.segChunks - 1) / p.segChunks); seg < p.S; ++seg) {
         for (int j = 0; j < NI; ++j) {
             const int i = i_lo + warp * NI + j;
-            if (i < N && half == 0) {
+            if (i < N && grp == 0) {
                 float* dst = p.partial + ((static_cast<size_t>(r) * p.S + seg) * N + i) * p.Bpad + 4 * q;
                 *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
-                *reinterpret_cast<float4*>(dst + 64) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4*>(dst + BT / 2) = make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
     }
 
-    // A CTA that gave up waits once more, again bounded, for the copy it abandoned before it leaves.
-    if (gave_up && c < c_end) mbar_wait_bounded(g_bar, static_cast<unsigned>(c - c_begin) & 1u);
+    // A thread that gave up waits once more, again bounded, for the copy it abandoned (the chunk it recorded
+    // when the copy was issued) before the CTA releases its shared memory.
+    if (pending >= 0) mbar_wait_bounded(g_bar, static_cast<unsigned>(pending - c_begin) & 1u);
     tmem_fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
@@ -796,14 +817,20 @@ __global__ void __launch_bounds__(THREADS, 1)
 
 struct FusedConfig {
     int bpl, ni, iparts, Bpad, R, entCap, segChunks, S;
+    int groups;  // lane groups per warp of the group kernel (2: batch 65..128, 4: batch <= 64), 0: ffi_bwd_fused_kernel
     size_t smem;
 };
+
+constexpr int kGroupThreads = 512, kGroupNI = 8;  // (1024 threads x 4 inputs was measured: 10 % slower)
 
 bool fused_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, FusedConfig* c) {
     if (!plan || !plan->has_chunks || B > 128) return false;
     if (plan->K >= (1 << (32 - kKShift))) return false;  // k shares the entry's code word with the row offset
-    c->bpl = B <= 32 ? 1 : (B <= 64 ? 2 : 4);
-    c->ni = 32 / c->bpl;  // 32 accumulator + 32 x registers per lane
+    // the group kernel's entry code holds the position within the chunk in 14 bits
+    const bool group_kernel = static_cast<long long>(plan->chunk_rows) * plan->K <= (1 << (32 - kKShift));
+    c->groups = group_kernel ? (B > 64 ? 2 : 4) : 0;
+    c->bpl = group_kernel ? (B > 64 ? 4 : 2) : (B <= 32 ? 1 : (B <= 64 ? 2 : 4));
+    c->ni = group_kernel ? kGroupNI : 32 / c->bpl;  // ffi_bwd_fused_kernel: 32 accumulator + 32 x registers per lane
     const int BT = 32 * c->bpl;
     const int width = kWarps * c->ni;  // inputs per slice: 128, 256 or 512
     c->iparts = static_cast<int>(ceil_div(plan->N, width));
@@ -822,8 +849,10 @@ bool fused_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, FusedC
     const size_t cap = static_cast<size_t>((plan->max_slice_entries[stat] + 7) / 8 * 8 + 8);
     const size_t T = static_cast<size_t>(plan->chunk_rows);
     if (T * BT * 4 > (size_t{1} << kKShift)) return false;
-    const size_t total = T * BT * 4 + 2 * cap * 8 + static_cast<size_t>(kWarps) * kSlots * kDRow * 4 +
-                         2 * (kWarps * c->ni + 1) * 4 + 16;
+    // the group kernel buffers 32 / groups steps per warp; + its barrier, TMEM slot and alignment slack
+    const size_t slots = group_kernel ? 32 / c->groups : kSlots;
+    const size_t total = T * BT * 4 + 2 * cap * 8 + static_cast<size_t>(kWarps) * slots * kDRow * 4 +
+                         2 * (kWarps * c->ni + 1) * 4 + 16 + (group_kernel ? 1024 : 0);
     if (total > static_cast<size_t>(dev.max_smem_optin)) return false;  // unusually dense slice or large K: separate kernels
     c->entCap = static_cast<int>(cap);
     c->smem = total;
@@ -831,7 +860,7 @@ bool fused_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, FusedC
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link libcuda).
-int encode_g_map(CUtensorMap* map, const float* gT, int64_t L, int64_t ldg, int chunk_rows) {
+int encode_g_map(CUtensorMap* map, const float* gT, int64_t L, int64_t ldg, int chunk_rows, int BT) {
     using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -843,11 +872,13 @@ int encode_g_map(CUtensorMap* map, const float* gT, int64_t L, int64_t ldg, int 
         if (q != cudaDriverEntryPointSuccess || !fn) return fail(FFI_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
         encode = reinterpret_cast<EncodeFn>(fn);
     }
-    if (reinterpret_cast<uintptr_t>(gT) % 16 != 0 || chunk_rows > 256)
+    if (reinterpret_cast<uintptr_t>(gT) % 16 != 0 || chunk_rows > 256 || (BT != 64 && BT != 128))
         return fail(FFI_ERR_INVALID_ARGUMENT, "transposed gradient must be 16-byte aligned, chunks at most 256 rows");
-    const cuuint64_t dims[2] = {128, static_cast<cuuint64_t>(L)};
+    // the stored rows may be narrower than the tile (batch <= 32 keeps 32 columns): the box's columns past them
+    // are filled with zeros, like its rows past L
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(ldg < BT ? ldg : BT), static_cast<cuuint64_t>(L)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldg) * 4};
-    const cuuint32_t box[2] = {128, static_cast<cuuint32_t>(chunk_rows)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(BT), static_cast<cuuint32_t>(chunk_rows)};
     const cuuint32_t elem[2] = {1, 1};
     const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(gT), dims, strides, box, elem,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -898,7 +929,9 @@ int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, floa
     const size_t need = static_cast<size_t>(c.R) * c.S * a.N * c.Bpad * 4;
     if (!a.workspace || a.workspace_bytes < need || reinterpret_cast<uintptr_t>(a.workspace) % 16 != 0)
         return fail(FFI_ERR_WORKSPACE, "fused backward needs %zu bytes of 16-byte aligned workspace", need);
-    if (!a.gT || a.ldg < c.Bpad || a.ldg % 32 != 0 || !xT)
+    // the group kernel's tile copy fills the columns past a narrower stored row with zeros
+    const int64_t min_ldg = c.groups ? round_up(a.B, 32) : c.Bpad;
+    if (!a.gT || a.ldg < min_ldg || a.ldg % 32 != 0 || !xT)
         return fail(FFI_ERR_INVALID_ARGUMENT, "fused backward needs gT and xT");
     BwdFusedParams p;
     p.W = a.W;
@@ -925,30 +958,31 @@ int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, floa
     p.entCap = c.entCap;
     p.segChunks = c.segChunks;
     p.S = c.S;
-    // the pair kernel's entry code holds the position within the chunk in 14 bits
-    const bool pairs = c.bpl == 4 && static_cast<long long>(a.plan->chunk_rows) * a.K <= (1 << (32 - kKShift));
+    const bool pairs = c.groups != 0;
     if (gbias && !pairs) {  // the other kernels leave grad_bias to a pass over gT
         rc = launch_bias_grad_rows(a.gT, a.ldg, a.L, gbias, stream);
         if (rc != FFI_OK) return rc;
     }
-    if (pairs) p.gbias = gbias;
-    if (c.bpl == 4 && !pairs) rc = launch_fused_t<8, 4>(p, c, stream);
-    else if (c.bpl == 4) {
-        // gT as a 2-D tensor [L rows][128 columns] with row pitch ldg; one box = the g tile of a chunk
+    if (pairs) {
+        p.gbias = gbias;
+        // gT as a 2-D tensor [L rows][BT columns] with row pitch ldg; one box = the g tile of a chunk
         CUtensorMap g_map;
-        rc = encode_g_map(&g_map, a.gT, a.L, a.ldg, a.plan->chunk_rows);
+        rc = encode_g_map(&g_map, a.gT, a.L, a.ldg, a.plan->chunk_rows, c.Bpad);
         if (rc != FFI_OK) return rc;
-        constexpr int PT = 512, PNI = 8, PSL = 16;  // (1024 threads x 4 inputs was measured: 10 % slower)
-        auto kern = ffi_bwd_pairs_kernel<PNI, PT, PSL>;
-        // as fused_config's total, with this variant's dot buffers; + barriers, TMEM slot, slack
-        const size_t smem = c.smem - static_cast<size_t>(kWarps) * kSlots * kDRow * 4 +
-                            static_cast<size_t>(PT / 32) * PSL * kDRow * 4 + 1024;
-        FFI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         dim3 grid(static_cast<unsigned>(c.R), static_cast<unsigned>(c.iparts), 1);
-        kern<<<grid, PT, smem, stream>>>(p, g_map);
+        if (c.groups == 2) {
+            auto kern = ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 16, 2>;
+            FFI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(c.smem)));
+            kern<<<grid, kGroupThreads, c.smem, stream>>>(p, g_map);
+        } else {
+            auto kern = ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 8, 4>;
+            FFI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(c.smem)));
+            kern<<<grid, kGroupThreads, c.smem, stream>>>(p, g_map);
+        }
         FFI_LAUNCH_CHECK("ffi_bwd_pairs_kernel");
         rc = FFI_OK;
     }
+    else if (c.bpl == 4) rc = launch_fused_t<8, 4>(p, c, stream);
     else if (c.bpl == 2) rc = launch_fused_t<16, 2>(p, c, stream);
     else rc = launch_fused_t<32, 1>(p, c, stream);
     if (rc != FFI_OK) return rc;

@@ -121,6 +121,7 @@ struct ffi_plan {
     int32_t* perm = nullptr;    // [L*K]   positions sorted by (idx[p], p)
     int32_t* cperm = nullptr;   // [L*K]   chunk-major: chunk c holds its T*K positions sorted by (idx[p], p)
     int32_t* cptr = nullptr;    // [n_chunks][N+1] offsets of each input's run inside its chunk
+    void* build_scratch = nullptr;  // sort scratch kept by ffi_plan_rebuild (none after ffi_plan_create alone)
     size_t device_bytes = 0;
 };
 

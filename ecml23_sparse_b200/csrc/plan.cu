@@ -51,9 +51,91 @@ __global__ void radix_hist_kernel(const int* __restrict__ keys, long long n, int
     }
 }
 
-// In-place exclusive scan of `data[0..n)` by one block; int64 running total, int32 output
-// (totals are bounded by L*K < 2^31).
-__global__ void exclusive_scan_kernel(int* __restrict__ data, long long n) {
+// In-place exclusive scan of `data[0..n)`: int64 running totals, int32 output (totals are bounded by
+// L*K < 2^31).  Three phases: every block adds up its segment of kScanSeg consecutive elements, one block
+// scans the segment totals, every block rescans its segment from its offset.
+constexpr int kScanThreads = 256;
+constexpr int kScanPer = 16;                          // consecutive elements per thread
+constexpr int kScanSeg = kScanThreads * kScanPer;     // elements per block
+
+__device__ __forceinline__ long long block_exclusive_scan(long long v, long long* sh, long long* total) {
+    // exclusive scan of one value per thread over the block (kScanThreads threads); *total = block sum
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    long long incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off *= 2) {
+        const long long up = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += up;
+    }
+    if (lane == 31) sh[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        long long w = lane < kScanThreads / 32 ? sh[lane] : 0;
+        long long wi = w;
+#pragma unroll
+        for (int off = 1; off < 32; off *= 2) {
+            const long long up = __shfl_up_sync(0xffffffffu, wi, off);
+            if (lane >= off) wi += up;
+        }
+        if (lane < kScanThreads / 32) sh[lane] = wi - w;
+        if (lane == kScanThreads / 32 - 1) sh[kScanThreads / 32] = wi;
+    }
+    __syncthreads();
+    *total = sh[kScanThreads / 32];
+    const long long res = sh[warp] + incl - v;
+    __syncthreads();
+    return res;
+}
+
+__global__ void __launch_bounds__(kScanThreads) scan_segment_sums_kernel(const int* __restrict__ data, long long n,
+                                                                        long long* __restrict__ seg_sums) {
+    __shared__ long long sh[kScanThreads / 32 + 1];
+    const long long base = static_cast<long long>(blockIdx.x) * kScanSeg + static_cast<long long>(threadIdx.x) * kScanPer;
+    long long s = 0;
+#pragma unroll
+    for (int u = 0; u < kScanPer; ++u)
+        if (base + u < n) s += data[base + u];
+    long long total;
+    block_exclusive_scan(s, sh, &total);
+    if (threadIdx.x == 0) seg_sums[blockIdx.x] = total;
+}
+
+// exclusive scan of the segment totals by one block (a few thousand values)
+__global__ void __launch_bounds__(kScanThreads) scan_totals_kernel(long long* __restrict__ seg_sums, long long nseg) {
+    __shared__ long long sh[kScanThreads / 32 + 1];
+    long long carry = 0;
+    for (long long b0 = 0; b0 < nseg; b0 += kScanThreads) {
+        const long long i = b0 + threadIdx.x;
+        const long long v = i < nseg ? seg_sums[i] : 0;
+        long long total;
+        const long long ex = block_exclusive_scan(v, sh, &total);
+        if (i < nseg) seg_sums[i] = carry + ex;
+        carry += total;
+    }
+}
+
+__global__ void __launch_bounds__(kScanThreads) scan_apply_kernel(int* __restrict__ data, long long n,
+                                                                 const long long* __restrict__ seg_offsets) {
+    __shared__ long long sh[kScanThreads / 32 + 1];
+    const long long base = static_cast<long long>(blockIdx.x) * kScanSeg + static_cast<long long>(threadIdx.x) * kScanPer;
+    int v[kScanPer];
+    long long s = 0;
+#pragma unroll
+    for (int u = 0; u < kScanPer; ++u) {
+        v[u] = base + u < n ? data[base + u] : 0;
+        s += v[u];
+    }
+    long long total;
+    long long run = seg_offsets[blockIdx.x] + block_exclusive_scan(s, sh, &total);
+#pragma unroll
+    for (int u = 0; u < kScanPer; ++u) {
+        if (base + u < n) data[base + u] = static_cast<int>(run);
+        run += v[u];
+    }
+}
+
+// The same scan by one block, for short arrays (the self-check export's N + 1 row totals).
+__global__ void small_exclusive_scan_kernel(int* __restrict__ data, long long n) {
     __shared__ long long sums[1024];
     const int t = threadIdx.x;
     const long long chunk = (n + blockDim.x - 1) / blockDim.x;
@@ -77,6 +159,16 @@ __global__ void exclusive_scan_kernel(int* __restrict__ data, long long n) {
         data[e] = static_cast<int>(run);
         run += v;
     }
+}
+
+// `seg_scratch` holds ceil(n / kScanSeg) int64 values.
+int launch_exclusive_scan(int* data, long long n, long long* seg_scratch, cudaStream_t stream) {
+    const long long nseg = ceil_div(n, kScanSeg);
+    scan_segment_sums_kernel<<<static_cast<unsigned>(nseg), kScanThreads, 0, stream>>>(data, n, seg_scratch);
+    scan_totals_kernel<<<1, kScanThreads, 0, stream>>>(seg_scratch, nseg);
+    scan_apply_kernel<<<static_cast<unsigned>(nseg), kScanThreads, 0, stream>>>(data, n, seg_scratch);
+    FFI_LAUNCH_CHECK("exclusive scan");
+    return FFI_OK;
 }
 
 // Stable scatter of one digit pass. vals_in == nullptr means "value = element index".
@@ -250,6 +342,121 @@ constexpr int64_t kNarrowMaxN = 2048;  // inputs the register-accumulator grad_x
 
 using namespace ffi;
 
+namespace ffi {
+namespace {
+
+constexpr size_t kScratchAlign = 256;
+size_t scratch_up(size_t v) { return (v + kScratchAlign - 1) / kScratchAlign * kScratchAlign; }
+
+// Geometry of a plan and the carving of its build scratch (one allocation).
+struct PlanLayout {
+    long long n, nTiles, scan_segs, nChunks, cptrBytes;
+    int T;
+    bool chunks;
+    size_t off_kA, off_vA, off_kB, off_vB, off_counts, off_bad, off_segs, off_lb, off_stats, total;
+};
+
+PlanLayout plan_layout(int64_t L, int64_t K, int64_t N) {
+    PlanLayout g;
+    g.n = L * K;
+    g.nTiles = ceil_div(g.n, kTile);
+    g.scan_segs = ceil_div(256 * g.nTiles > N + 1 ? 256 * g.nTiles : N + 1, kScanSeg);
+    g.T = plan_chunk_rows(K);
+    g.nChunks = ceil_div(L, g.T > 0 ? g.T : 1);
+    g.cptrBytes = g.nChunks * (N + 1) * 4;
+    g.chunks = g.T >= 8 && N <= kNarrowMaxN && g.cptrBytes <= (512LL << 20) && static_cast<long long>(g.T) * K <= 65536;
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t at = off;
+        off += scratch_up(bytes ? bytes : 4);
+        return at;
+    };
+    g.off_kA = take(g.n * 4);
+    g.off_vA = take(g.n * 4);
+    g.off_kB = take(g.n * 4);
+    g.off_vB = take(g.n * 4);
+    g.off_counts = take(256 * g.nTiles * 4);
+    g.off_bad = take(4);
+    g.off_segs = take(g.scan_segs * 8);
+    g.off_lb = take(g.chunks ? (g.nChunks + 1) * N * 4 : 4);
+    g.off_stats = take(4 * sizeof(int));
+    g.total = off;
+    return g;
+}
+
+// Fills the (already allocated) arrays of `plan` from `idx`; `scratch` holds plan_layout(...).total bytes.
+// Synchronises the stream (index validation, slice statistics).
+int plan_build(ffi_plan* plan, const int32_t* idx, unsigned char* scratch, cudaStream_t stream) {
+    const int64_t L = plan->L, K = plan->K, N = plan->N;
+    const PlanLayout g = plan_layout(L, K, N);
+    const long long n = g.n, nTiles = g.nTiles;
+    int* kA = reinterpret_cast<int*>(scratch + g.off_kA);
+    int* vA = reinterpret_cast<int*>(scratch + g.off_vA);
+    int* kB = reinterpret_cast<int*>(scratch + g.off_kB);
+    int* vB = reinterpret_cast<int*>(scratch + g.off_vB);
+    int* counts = reinterpret_cast<int*>(scratch + g.off_counts);
+    int* bad = reinterpret_cast<int*>(scratch + g.off_bad);
+    long long* segs = reinterpret_cast<long long*>(scratch + g.off_segs);
+    int* lb = reinterpret_cast<int*>(scratch + g.off_lb);
+    int* stats = reinterpret_cast<int*>(scratch + g.off_stats);
+
+    FFI_CUDA_CHECK(cudaMemsetAsync(bad, 0, 4, stream));
+    validate_idx_kernel<<<1024, 256, 0, stream>>>(idx, n, static_cast<int>(N), bad);
+    int h_bad = 0;
+    FFI_CUDA_CHECK(cudaMemcpyAsync(&h_bad, bad, 4, cudaMemcpyDeviceToHost, stream));
+    FFI_CUDA_CHECK(cudaStreamSynchronize(stream));
+    if (h_bad) return fail(FFI_ERR_INDEX_RANGE, "idx holds a value outside [0, %lld)", (long long)N);
+
+    const int passes = (significant_bits(N) + 7) / 8;
+    const unsigned sortBlocks = static_cast<unsigned>(ceil_div(nTiles, kSortWarps));
+    const int* kin = idx;
+    const int* vin = nullptr;
+    int* kout = kA;
+    int* vout = vA;
+    for (int pass = 0; pass < passes; ++pass) {
+        const int shift = 8 * pass;
+        radix_hist_kernel<<<sortBlocks, 32 * kSortWarps, 0, stream>>>(kin, n, shift, counts, nTiles);
+        const int src = launch_exclusive_scan(counts, 256 * nTiles, segs, stream);
+        if (src != FFI_OK) return src;
+        radix_scatter_kernel<<<sortBlocks, 32 * kSortWarps, 0, stream>>>(kin, vin, kout, vout, n, shift, counts, nTiles);
+        kin = kout;
+        vin = vout;
+        const bool toB = (kout == kA);
+        kout = toB ? kB : kA;
+        vout = toB ? vB : vA;
+    }
+    FFI_LAUNCH_CHECK("radix sort");
+    rowptr_kernel<<<static_cast<unsigned>(ceil_div(N + 1, 256)), 256, 0, stream>>>(kin, n, static_cast<int>(N),
+                                                                                   plan->rowptr);
+    FFI_CUDA_CHECK(cudaMemcpyAsync(plan->perm, vin, n * 4, cudaMemcpyDeviceToDevice, stream));
+    FFI_LAUNCH_CHECK("rowptr_kernel");
+
+    // Chunked lists for the narrow-input grad_x kernel.
+    if (g.chunks) {
+        const long long chunkEntries = static_cast<long long>(g.T) * K;
+        const long long nb = (g.nChunks + 1) * N;
+        chunk_bounds_kernel<<<static_cast<unsigned>(ceil_div(nb, 256)), 256, 0, stream>>>(
+            plan->rowptr, plan->perm, static_cast<int>(N), chunkEntries, g.nChunks, lb);
+        chunk_fill_kernel<<<static_cast<unsigned>(g.nChunks), 256, (N + 1) * sizeof(int), stream>>>(
+            plan->perm, lb, static_cast<int>(N), chunkEntries, plan->cptr, plan->cperm);
+        FFI_LAUNCH_CHECK("chunk kernels");
+        // slice statistics for the kernels that stage one slice of a chunk in shared memory
+        FFI_CUDA_CHECK(cudaMemsetAsync(stats, 0, 4 * sizeof(int), stream));
+        slice_stats_kernel<<<static_cast<unsigned>(ceil_div(g.nChunks, 256)), 256, 0, stream>>>(
+            plan->cptr, static_cast<int>(N), g.nChunks, stats);
+        FFI_LAUNCH_CHECK("slice_stats_kernel");
+        FFI_CUDA_CHECK(cudaMemcpyAsync(plan->max_slice_entries, stats, 4 * sizeof(int), cudaMemcpyDeviceToHost, stream));
+        plan->chunk_rows = g.T;
+        plan->n_chunks = g.nChunks;
+        plan->has_chunks = true;
+    }
+    FFI_CUDA_CHECK(cudaStreamSynchronize(stream));
+    return FFI_OK;
+}
+
+}  // namespace
+}  // namespace ffi
+
 extern "C" int ffi_plan_create(const int32_t* idx, int64_t L, int64_t K, int64_t N, void* stream_v,
                                ffi_plan** out_plan) {
     if (!out_plan) return fail(FFI_ERR_INVALID_ARGUMENT, "out_plan is NULL");
@@ -259,7 +466,6 @@ extern "C" int ffi_plan_create(const int32_t* idx, int64_t L, int64_t K, int64_t
     if (N >= (1LL << 31) || L * K >= (1LL << 31) - kTile)
         return fail(FFI_ERR_UNSUPPORTED, "L*K=%lld (or N) does not fit 32-bit positions", (long long)(L * K));
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    const long long n = L * K;
 
     // Owns the half-built plan: every early return below (the CUDA check macros included) frees
     // the plan and its device arrays; success hands it to the caller.
@@ -274,96 +480,47 @@ extern "C" int ffi_plan_create(const int32_t* idx, int64_t L, int64_t K, int64_t
     plan->K = K;
     plan->N = N;
     FFI_CUDA_CHECK(cudaGetDevice(&plan->device));
-    auto cleanup = [&](int rc) { return rc; };
+    const PlanLayout g = plan_layout(L, K, N);
 
     if (cudaMalloc(&plan->rowptr, (N + 1) * sizeof(int)) != cudaSuccess ||
-        cudaMalloc(&plan->perm, n * sizeof(int)) != cudaSuccess) {
+        cudaMalloc(&plan->perm, g.n * sizeof(int)) != cudaSuccess) {
         cudaGetLastError();
-        return cleanup(fail(FFI_ERR_ALLOC, "cudaMalloc of the transposed index failed"));
+        return fail(FFI_ERR_ALLOC, "cudaMalloc of the transposed index failed");
     }
-    plan->device_bytes = (N + 1) * sizeof(int) + n * sizeof(int);
-
-    const long long nTiles = ceil_div(n, kTile);
-    DeviceBuffer kA, vA, kB, vB, counts, bad;
-    if (kA.alloc(n * 4) != cudaSuccess || vA.alloc(n * 4) != cudaSuccess || kB.alloc(n * 4) != cudaSuccess ||
-        vB.alloc(n * 4) != cudaSuccess || counts.alloc(256 * nTiles * 4) != cudaSuccess ||
-        bad.alloc(4) != cudaSuccess) {
+    plan->device_bytes = (N + 1) * sizeof(int) + g.n * sizeof(int);
+    if (g.chunks) {
+        if (cudaMalloc(&plan->cptr, g.cptrBytes) != cudaSuccess || cudaMalloc(&plan->cperm, g.n * 4) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(FFI_ERR_ALLOC, "cudaMalloc of the chunked index failed");
+        }
+        plan->device_bytes += g.cptrBytes + g.n * 4;
+    }
+    DeviceBuffer scratch;
+    if (scratch.alloc(g.total) != cudaSuccess) {
         cudaGetLastError();
-        return cleanup(fail(FFI_ERR_ALLOC, "cudaMalloc of sort scratch failed"));
+        return fail(FFI_ERR_ALLOC, "cudaMalloc of sort scratch failed");
     }
-
-    FFI_CUDA_CHECK(cudaMemsetAsync(bad.ptr, 0, 4, stream));
-    validate_idx_kernel<<<1024, 256, 0, stream>>>(idx, n, static_cast<int>(N), bad.as<int>());
-    int h_bad = 0;
-    FFI_CUDA_CHECK(cudaMemcpyAsync(&h_bad, bad.ptr, 4, cudaMemcpyDeviceToHost, stream));
-    FFI_CUDA_CHECK(cudaStreamSynchronize(stream));
-    if (h_bad) return cleanup(fail(FFI_ERR_INDEX_RANGE, "idx holds a value outside [0, %lld)", (long long)N));
-
-    const int passes = (significant_bits(N) + 7) / 8;
-    const unsigned sortBlocks = static_cast<unsigned>(ceil_div(nTiles, kSortWarps));
-    const int* kin = idx;
-    const int* vin = nullptr;
-    int* kout = kA.as<int>();
-    int* vout = vA.as<int>();
-    for (int pass = 0; pass < passes; ++pass) {
-        const int shift = 8 * pass;
-        radix_hist_kernel<<<sortBlocks, 32 * kSortWarps, 0, stream>>>(kin, n, shift, counts.as<int>(), nTiles);
-        exclusive_scan_kernel<<<1, 1024, 0, stream>>>(counts.as<int>(), 256 * nTiles);
-        radix_scatter_kernel<<<sortBlocks, 32 * kSortWarps, 0, stream>>>(kin, vin, kout, vout, n, shift,
-                                                                          counts.as<int>(), nTiles);
-        kin = kout;
-        vin = vout;
-        const bool toB = (kout == kA.as<int>());
-        kout = toB ? kB.as<int>() : kA.as<int>();
-        vout = toB ? vB.as<int>() : vA.as<int>();
-    }
-    FFI_LAUNCH_CHECK("radix sort");
-    rowptr_kernel<<<static_cast<unsigned>(ceil_div(N + 1, 256)), 256, 0, stream>>>(kin, n, static_cast<int>(N),
-                                                                                   plan->rowptr);
-    FFI_CUDA_CHECK(cudaMemcpyAsync(plan->perm, vin, n * 4, cudaMemcpyDeviceToDevice, stream));
-    FFI_LAUNCH_CHECK("rowptr_kernel");
-
-    // Chunked lists for the narrow-input grad_x kernel.
-    const int T = plan_chunk_rows(K);
-    const long long nChunks = ceil_div(L, T > 0 ? T : 1);
-    const long long cptrBytes = nChunks * (N + 1) * 4;
-    if (T >= 8 && N <= kNarrowMaxN && cptrBytes <= (512LL << 20) && static_cast<long long>(T) * K <= 65536) {
-        DeviceBuffer lb;
-        if (lb.alloc((nChunks + 1) * N * 4) != cudaSuccess ||
-            cudaMalloc(&plan->cptr, cptrBytes) != cudaSuccess ||
-            cudaMalloc(&plan->cperm, n * 4) != cudaSuccess) {
-            cudaGetLastError();
-            return cleanup(fail(FFI_ERR_ALLOC, "cudaMalloc of the chunked index failed"));
-        }
-        plan->device_bytes += cptrBytes + n * 4;
-        const long long chunkEntries = static_cast<long long>(T) * K;
-        const long long nb = (nChunks + 1) * N;
-        chunk_bounds_kernel<<<static_cast<unsigned>(ceil_div(nb, 256)), 256, 0, stream>>>(
-            plan->rowptr, plan->perm, static_cast<int>(N), chunkEntries, nChunks, lb.as<int>());
-        chunk_fill_kernel<<<static_cast<unsigned>(nChunks), 256, (N + 1) * sizeof(int), stream>>>(
-            plan->perm, lb.as<int>(), static_cast<int>(N), chunkEntries, plan->cptr, plan->cperm);
-        FFI_LAUNCH_CHECK("chunk kernels");
-        // slice statistics for the kernels that stage one slice of a chunk in shared memory
-        DeviceBuffer stats;
-        if (stats.alloc(4 * sizeof(int)) != cudaSuccess) {
-            cudaGetLastError();
-            return cleanup(fail(FFI_ERR_ALLOC, "cudaMalloc of plan statistics failed"));
-        }
-        FFI_CUDA_CHECK(cudaMemsetAsync(stats.ptr, 0, 4 * sizeof(int), stream));
-        slice_stats_kernel<<<static_cast<unsigned>(ceil_div(nChunks, 256)), 256, 0, stream>>>(
-            plan->cptr, static_cast<int>(N), nChunks, stats.as<int>());
-        FFI_LAUNCH_CHECK("slice_stats_kernel");
-        FFI_CUDA_CHECK(cudaMemcpyAsync(plan->max_slice_entries, stats.ptr, 4 * sizeof(int), cudaMemcpyDeviceToHost,
-                                       stream));
-        FFI_CUDA_CHECK(cudaStreamSynchronize(stream));
-        plan->chunk_rows = T;
-        plan->n_chunks = nChunks;
-        plan->has_chunks = true;
-    }
-    FFI_CUDA_CHECK(cudaStreamSynchronize(stream));
+    const int rc = plan_build(plan, idx, scratch.as<unsigned char>(), stream);
+    if (rc != FFI_OK) return rc;
     owner.p = nullptr;
     *out_plan = plan;
     return FFI_OK;
+}
+
+extern "C" int ffi_plan_rebuild(ffi_plan* plan, const int32_t* idx, void* stream_v) {
+    if (!plan || !idx) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL argument to ffi_plan_rebuild");
+    int rc = check_plan_device(plan);
+    if (rc != FFI_OK) return rc;
+    const PlanLayout g = plan_layout(plan->L, plan->K, plan->N);
+    if (!plan->build_scratch) {
+        if (cudaMalloc(&plan->build_scratch, g.total) != cudaSuccess) {
+            cudaGetLastError();
+            plan->build_scratch = nullptr;
+            return fail(FFI_ERR_ALLOC, "cudaMalloc of the plan's sort scratch failed");
+        }
+        plan->device_bytes += g.total;
+    }
+    return plan_build(plan, idx, static_cast<unsigned char*>(plan->build_scratch), static_cast<cudaStream_t>(stream_v));
 }
 
 extern "C" int ffi_plan_destroy(ffi_plan* plan) {
@@ -372,6 +529,7 @@ extern "C" int ffi_plan_destroy(ffi_plan* plan) {
     if (plan->perm) cudaFree(plan->perm);
     if (plan->cperm) cudaFree(plan->cperm);
     if (plan->cptr) cudaFree(plan->cptr);
+    if (plan->build_scratch) cudaFree(plan->build_scratch);
     delete plan;
     return FFI_OK;
 }
@@ -404,7 +562,7 @@ extern "C" int ffi_plan_export_chunked(const ffi_plan* plan, int32_t* rowptr, in
     const int N = static_cast<int>(plan->N);
     chunked_row_totals_kernel<<<static_cast<unsigned>(ceil_div(N + 1, 256)), 256, 0, stream>>>(
         plan->cptr, N, plan->n_chunks, rowptr);
-    exclusive_scan_kernel<<<1, 1024, 0, stream>>>(rowptr, N + 1);
+    small_exclusive_scan_kernel<<<1, 1024, 0, stream>>>(rowptr, N + 1);
     chunked_gather_kernel<<<static_cast<unsigned>(ceil_div(N, 4)), 128, 0, stream>>>(
         plan->cptr, plan->cperm, rowptr, N, plan->n_chunks,
         static_cast<long long>(plan->chunk_rows) * plan->K, perm);

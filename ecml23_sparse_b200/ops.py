@@ -92,7 +92,19 @@ class FFIPlan:
             _lib.check(_lib.load().ffi_plan_create(lookup.data_ptr(), self.L, self.K, self.N,
                                                    _stream_ptr(self.device), ctypes.byref(handle)))
         self._handle = handle
+        self.builds = 1
         self._finalizer = weakref.finalize(self, _lib.load().ffi_plan_destroy, handle)
+
+    def rebuild(self, lookup: torch.Tensor) -> "FFIPlan":
+        """Re-derives the plan in place from a table of the same shape whose contents changed (rewiring);
+        the index arrays are reused and, from the second rebuild on, nothing is allocated."""
+        lookup = _as_index(lookup)
+        if tuple(lookup.shape) != (self.L, self.K) or lookup.device != self.device:
+            raise ValueError("rebuild needs a table of the plan's shape on the plan's device")
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().ffi_plan_rebuild(self._handle, lookup.data_ptr(), _stream_ptr(self.device)))
+        self.builds += 1
+        return self
 
     @property
     def handle(self):
@@ -121,13 +133,18 @@ def get_plan(lookup: torch.Tensor, n_in: int) -> FFIPlan:
     """Plan for `lookup`, cached per (storage address, shape, tensor version).
 
     An in-place update of the table (rewiring) bumps the tensor's version and leads to a
-    rebuild.  The cache keeps a reference to the table so that its address cannot be handed
-    to another tensor while the entry lives (at most 8 tables are kept).
+    rebuild of the cached plan in place (`FFIPlan.rebuild`: same object, new contents).  The cache
+    keeps a reference to the table so that its address cannot be handed to another tensor while
+    the entry lives (at most 8 tables are kept).
     """
     key = (lookup.data_ptr(), tuple(lookup.shape), int(n_in), lookup.device.index)
     hit = _plan_cache.get(key)
     if hit is not None and hit[0] == lookup._version:
         return hit[1]
+    if hit is not None:
+        plan = hit[1].rebuild(lookup)
+        _plan_cache[key] = (lookup._version, plan, lookup)
+        return plan
     plan = FFIPlan(lookup, n_in)
     _plan_cache.pop(key, None)
     if len(_plan_cache) >= _PLAN_CACHE_MAX:

@@ -83,6 +83,15 @@ int ffi_forward(const void* x, const int32_t* idx, const void* W, const float* b
 int ffi_plan_create(const int32_t* idx, int64_t L, int64_t K, int64_t N, void* stream,
                     ffi_plan** out_plan);
 
+/*
+ * Rebuilds `plan` in place from a table of the same (L, K, N) whose contents changed (after a rewiring
+ * step): same result as destroying it and calling ffi_plan_create, without allocating or freeing the
+ * index arrays.  The first rebuild of a plan allocates its sort scratch (about 17 bytes per connection)
+ * and keeps it until ffi_plan_destroy; later rebuilds allocate nothing.  Synchronises `stream`.
+ * FFI_ERR_INDEX_RANGE leaves the plan unusable until a rebuild succeeds.
+ */
+int ffi_plan_rebuild(ffi_plan* plan, const int32_t* idx, void* stream);
+
 int ffi_plan_destroy(ffi_plan* plan);
 
 /* Host-side description of a plan. Any out pointer may be NULL. */

@@ -57,6 +57,7 @@ def test_rewire_step_matches_host_restatement(cuda_device, shape, fraction):
     m_h, v_h = opt.m[0].cpu().numpy().copy(), opt.v[0].cpu().numpy().copy()
     version = layer.kernel_indices._version
     plan_before = layer.plan()
+    plan_before.rebuild(layer.lookup())  # a first in-place rebuild allocates the plan's sort scratch
 
     thr, count = layer.rewire(fraction, optimizer=opt, seed=11)
     thr_ref, sel = numpy_rewire(w_h, idx_h, m_h, v_h, n_in, fraction, seed=11)
@@ -71,8 +72,9 @@ def test_rewire_step_matches_host_restatement(cuda_device, shape, fraction):
         assert sel.size <= _num_selected(fraction, n) - 1 + 0                     # strict "<": the threshold stays
         assert layer.kernel_indices._version > version
         # the cached plan is stale now; the next one is rebuilt from the new table, bit-exact
+        builds = plan_before.builds
         plan_after = layer.plan()
-        assert plan_after is not plan_before
+        assert plan_after is plan_before and plan_after.builds == builds + 1   # rebuilt in place
         rowptr, perm = plan_after.export()
         exp_rowptr, exp_perm = oracle.transpose_index(idx_h.reshape(units, fan_in), n_in)
         assert np.array_equal(rowptr.cpu().numpy(), exp_rowptr)
