@@ -58,6 +58,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the extra shapes measured after the headline legs")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch the resident step kernel by kernel instead of replaying it as one CUDA graph")
     ap.add_argument("--reps", type=int, default=REPS, help="repetitions of the timed loop (median is reported)")
     return ap.parse_args()
 
@@ -411,26 +413,72 @@ def run_ours(args):
         if ok.item() == 1:
             resident_mode = "multimem"
 
-    def step_resident():
+    def compute_resident():
+        """The rank's own kernels: forward, backward of its shard (grad_x partial into the exchange buffer)."""
         y = ops._forward(xT, idx, W, bias, True)
         if resident_mode == "multimem":
             slot = peer.buf[0]
             _, gW, gb = ops._backward(xT, idx, W, g, True, plan=plan, want_bias_grad=True,
                                       feature_grad_out=slot[:N * B])
-            torch.ops.symm_mem.multimem_all_reduce_(slot, "sum", dist.group.WORLD.group_name)
             gx = slot[:N * B].view(N, B)
         elif resident_mode == "peer":
             _, gW, gb = ops._backward(xT, idx, W, g, True, plan=plan, want_bias_grad=True,
                                       feature_grad_out=peer.slot()[:N * B])
-            gx = peer.sum(peer_out)[:N * B].view(N, B)
+            gx = None
         else:
             gx, gW, gb = ops._backward(xT, idx, W, g, True, plan=plan, want_bias_grad=True)
-            if world > 1:
-                dist.all_reduce(gx)
         return y, gx, gW, gb
+
+    def exchange_resident(outs):
+        """Sum of the ranks' grad_x partials, in place where the mode allows it."""
+        y, gx, gW, gb = outs
+        if resident_mode == "multimem":
+            torch.ops.symm_mem.multimem_all_reduce_(peer.buf[0], "sum", dist.group.WORLD.group_name)
+        elif resident_mode == "peer":
+            gx = peer.sum(peer_out)[:N * B].view(N, B)
+        elif world > 1:
+            dist.all_reduce(gx)
+        return y, gx, gW, gb
+
+    def step_resident():
+        return exchange_resident(compute_resident())
 
     # forward, transposition of g, fused grad_x + grad_W, reduction of grad_x partials (+ the peer sum)
     launches_per_step = 4 + (1 if resident_mode == "peer" else 0)
+
+    # The rank's own kernels of a step are captured once into a CUDA graph and replayed: the same kernels on
+    # the same buffers, without the host's per-launch cost between them (at 8 GPUs a rank's step is 0.25 ms,
+    # so a few microseconds per launch gap count).  The exchange between the ranks is launched after the
+    # replay, outside the graph.  ffi_peer_sum's mode writes into alternating slots, which a replay cannot
+    # alternate, so that mode stays kernel by kernel.  All ranks take the same decision.
+    step_timed, graphed, graph = step_resident, False, None
+    if not args.no_graph and resident_mode != "peer":
+        ok = torch.ones(1, device=dev)
+        try:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    compute_resident()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                graph_out = compute_resident()
+            torch.cuda.synchronize()
+        except Exception as exc:  # noqa: BLE001 - capture is an optimisation: fall back to plain launches
+            print(f"bench: CUDA graph capture failed on rank {rank}: {exc!r}", file=sys.stderr, flush=True)
+            ok.zero_()
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 1:
+            graphed = True
+
+            def step_timed():
+                graph.replay()
+                return exchange_resident(graph_out)
+        else:
+            graph = None
 
     def timed_loop(fn, steps, warmup):
         for _ in range(warmup):
@@ -485,7 +533,7 @@ def run_ours(args):
     # The exchanged grad_x must equal NCCL's all-reduce of the same partials, whatever exchange was picked.
     check = None
     if world > 1:
-        check = verify_exchange(lambda: [step_resident()[1]],
+        check = verify_exchange(lambda: [step_timed()[1]],
                                 lambda: [ops._backward(xT, idx, W, g, True, plan=plan)[0]])
 
     def median_loop(fn):
@@ -494,7 +542,7 @@ def run_ours(args):
         runs.sort(key=lambda r: r[0])
         return runs[len(runs) // 2], [r[0] / args.steps for r in runs]
 
-    (total_ms, t0, t1), resident_reps = median_loop(step_resident)
+    (total_ms, t0, t1), resident_reps = median_loop(step_timed)
     ms_per_step = total_ms / args.steps
     value = B / (ms_per_step * 1e-3)
 
@@ -658,7 +706,7 @@ def run_ours(args):
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": dict(workload_config(B, N, L, K, world),
+            "config": dict(workload_config(B, N, L, K, world), launch="the rank's kernels of a step replayed as one CUDA graph, then the exchange" if graphed else "kernel by kernel",
                            **({"collective": {"resident": {"peer": "ffi_peer_sum", "nccl": "NCCL all-reduce",
                                                            "multimem": "in-switch (NVLS) all-reduce of torch symmetric memory"
                                                            }[resident_mode],
@@ -670,6 +718,8 @@ def run_ours(args):
             "wait_timeouts": wait_timeouts, "check": check, "extra": extra,
         }
         print(json.dumps(line), flush=True)
+    graph = None  # the captured step goes before the process group does
+    torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -36,6 +36,7 @@ EXPORTED_SYMBOLS = (
     "ffi_grad_x_static_max_scratch_bytes", "ffi_grad_x_static",
     "ffi_transposed_gradient_stride", "ffi_transpose_gradient",
     "ffi_backward_from_transposed", "ffi_forward_bce_workspace_bytes", "ffi_forward_bce", "ffi_forward_loss", "ffi_wait_timeouts",
+    "ffi_set_wait_limit_ticks",
     "ffi_forward_topk_workspace_bytes", "ffi_forward_topk", "ffi_peer_sum",
     "ffi_bce_workspace_bytes", "ffi_bce_grad", "ffi_adam_step",
     "ffi_rewire_workspace_bytes", "ffi_rewire",
@@ -101,6 +102,8 @@ def _declare(lib):
     lib.ffi_forward_topk.argtypes = [vp, vp, vp, vp, vp, vp, i32, i64, i64, i64, i64, i64, i32, i32, vp, sz, vp]
     lib.ffi_peer_sum.restype = i32
     lib.ffi_peer_sum.argtypes = [vp, vp, i32, i32, i64, ctypes.c_uint32, vp, vp]
+    lib.ffi_set_wait_limit_ticks.restype = i32
+    lib.ffi_set_wait_limit_ticks.argtypes = [i64]
     lib.ffi_wait_timeouts.restype = i32
     lib.ffi_wait_timeouts.argtypes = [vp]
     lib.ffi_bce_workspace_bytes.restype = sz

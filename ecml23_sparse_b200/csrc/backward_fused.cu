@@ -28,8 +28,10 @@
 
 namespace ffi {
 int peer_wait_timeouts(int* out);  // peer_reduce.cu
+int set_peer_wait_limit(long long ticks);
 namespace {
 __device__ int g_wait_timeouts = 0;  // bounded waits of this file's kernels that gave up
+__device__ long long g_wait_limit = 4000000000ll;  // clock64 ticks a wait may last (about two seconds)
 
 constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
@@ -448,8 +450,9 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
 __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
+    const long long limit = g_wait_limit;
     while (!mbar_try_wait(bar, parity))
-        if (clock64() - start > 4000000000ll) return false;
+        if (clock64() - start > limit) return false;
     return true;
 }
 
@@ -990,6 +993,15 @@ int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, floa
 }
 
 }  // namespace ffi
+
+// Test hook: how long (clock64 ticks of the current device, about 0.5 ns each) the bounded device-side waits
+// may last before they give up.  The default is about two seconds; a test of the give-up path lowers it.
+extern "C" int ffi_set_wait_limit_ticks(int64_t ticks) {
+    if (ticks < 1000) return ffi::fail(FFI_ERR_INVALID_ARGUMENT, "the wait limit must be at least 1000 ticks");
+    const long long t = ticks;
+    FFI_CUDA_CHECK(cudaMemcpyToSymbol(ffi::g_wait_limit, &t, sizeof(t)));
+    return ffi::set_peer_wait_limit(t);
+}
 
 // Number of bounded device-side waits that gave up since the library was loaded (0 in a healthy
 // run; any other value means the results of the affected call are void).  Synchronises the device.

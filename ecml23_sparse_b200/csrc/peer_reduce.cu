@@ -19,6 +19,7 @@ namespace ffi {
 namespace {
 
 __device__ int g_peer_timeouts = 0;  // waits on other GPUs that gave up (added into ffi_wait_timeouts)
+__device__ long long g_peer_wait_limit = 4000000000ll;  // clock64 ticks a wait may last (about two seconds)
 
 constexpr int kMaxPeers = 16;
 
@@ -40,6 +41,24 @@ __device__ __forceinline__ void store_flag(unsigned* p, unsigned v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// out[i] = sum over ranks of their partial, in rank order; all WORLD loads of an element are issued before
+// the first add, so one round trip over NVLink covers them all.
+template <int WORLD>
+__device__ __forceinline__ void add_partials(const PeerParams& p, int par) {
+    const long long n4 = p.n / 4;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 v[WORLD];
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r)
+            v[r] = reinterpret_cast<const float4*>(p.bufs[r] + static_cast<size_t>(par) * p.n)[i];
+        float4 s = v[0];
+#pragma unroll
+        for (int r = 1; r < WORLD; ++r) s.x += v[r].x, s.y += v[r].y, s.z += v[r].z, s.w += v[r].w;
+        reinterpret_cast<float4*>(p.out)[i] = s;
+    }
+}
+
 __global__ void __launch_bounds__(256) peer_sum_kernel(PeerParams p) {
     const int par = static_cast<int>(p.step & 1u);
     // 1. tell every rank (myself included) that my partial of this step is in place
@@ -52,8 +71,9 @@ __global__ void __launch_bounds__(256) peer_sum_kernel(PeerParams p) {
         const unsigned* f = p.flags[p.rank] + par * p.world + threadIdx.x;
         if (static_cast<int>(load_flag(f) - p.step) < 0) {
             const long long start = clock64();
+            const long long limit = g_peer_wait_limit;
             while (static_cast<int>(load_flag(f) - p.step) < 0) {
-                if (clock64() - start > 4000000000ll) {
+                if (clock64() - start > limit) {
                     atomicAdd(&g_peer_timeouts, 1);
                     break;
                 }
@@ -61,16 +81,24 @@ __global__ void __launch_bounds__(256) peer_sum_kernel(PeerParams p) {
         }
     }
     __syncthreads();
-    // 3. add the partials in rank order
-    const long long n4 = p.n / 4;
-    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
-        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < p.world; ++r) {
-            const float4 v = reinterpret_cast<const float4*>(p.bufs[r] + static_cast<size_t>(par) * p.n)[i];
-            s.x += v.x, s.y += v.y, s.z += v.z, s.w += v.w;
+    // 3. add the partials in rank order (0 + v0 + v1 + ... with the first term exact: same bits as a running sum)
+    switch (p.world) {
+        case 1: add_partials<1>(p, par); break;
+        case 2: add_partials<2>(p, par); break;
+        case 4: add_partials<4>(p, par); break;
+        case 8: add_partials<8>(p, par); break;
+        default: {
+            const long long n4 = p.n / 4;
+            const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+            for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+                float4 s = reinterpret_cast<const float4*>(p.bufs[0] + static_cast<size_t>(par) * p.n)[i];
+                for (int r = 1; r < p.world; ++r) {
+                    const float4 v = reinterpret_cast<const float4*>(p.bufs[r] + static_cast<size_t>(par) * p.n)[i];
+                    s.x += v.x, s.y += v.y, s.z += v.z, s.w += v.w;
+                }
+                reinterpret_cast<float4*>(p.out)[i] = s;
+            }
         }
-        reinterpret_cast<float4*>(p.out)[i] = s;
     }
 }
 
@@ -78,6 +106,11 @@ __global__ void __launch_bounds__(256) peer_sum_kernel(PeerParams p) {
 
 int peer_wait_timeouts(int* out) {
     FFI_CUDA_CHECK(cudaMemcpyFromSymbol(out, g_peer_timeouts, sizeof(int)));
+    return FFI_OK;
+}
+
+int set_peer_wait_limit(long long ticks) {
+    FFI_CUDA_CHECK(cudaMemcpyToSymbol(g_peer_wait_limit, &ticks, sizeof(ticks)));
     return FFI_OK;
 }
 
@@ -106,7 +139,7 @@ extern "C" int ffi_peer_sum(const void* const* peer_bufs, void* const* peer_flag
     p.step = step;
     const long long n4 = n / 4;
     long long blocks = (n4 + 255) / 256;
-    if (blocks > 64) blocks = 64;  // all blocks resident at once: none of them waits for another block
+    if (blocks > 128) blocks = 128;  // all blocks resident at once (fewer than SMs): none of them waits for another block
     peer_sum_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream_v)>>>(p);
     FFI_LAUNCH_CHECK("peer_sum_kernel");
     return FFI_OK;

@@ -264,6 +264,13 @@ int ffi_peer_sum(const void* const* peer_bufs, void* const* peer_flags, int rank
  */
 int ffi_wait_timeouts(int* out);
 
+/*
+ * Test hook: sets how long the bounded waits above may last on the current device, in clock64 ticks
+ * (about 0.5 ns each; the default, 4e9, is about two seconds; at least 1000).  A test of the give-up path
+ * lowers it so that a wait nothing will ever satisfy ends after a millisecond.  No counterpart in the reference.
+ */
+int ffi_set_wait_limit_ticks(int64_t ticks);
+
 /* ------------------------------------------------------------ loss / Adam ---- */
 
 /*

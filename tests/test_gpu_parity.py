@@ -346,7 +346,45 @@ def test_peer_sum_single_rank_and_argument_checks(cuda_device):
     assert lib.ffi_peer_sum(None, flgs, 0, 1, n, 1, out.data_ptr(), stream) == 1
     count = ctypes.c_int(-1)
     _lib.check(lib.ffi_wait_timeouts(ctypes.byref(count)))
-    assert count.value == 0
+    import cases
+    assert count.value == cases.EXPECTED_WAIT_TIMEOUTS
+
+
+def test_bounded_peer_wait_gives_up_and_is_counted(cuda_device):
+    """A wait on another GPU that nothing will ever satisfy: a world of two ranks of which only rank 0
+    exists.  With the limit lowered to about a millisecond the kernel must return by itself, leave the
+    context usable and be counted by ffi_wait_timeouts (the host-visible error status of the wait)."""
+    import ctypes
+    import time
+
+    import cases
+
+    dev = cuda_device
+    lib = _lib.load()
+    n = 1024
+    bufs = [torch.zeros((2, n), device=dev) for _ in range(2)]
+    flags = [torch.zeros((2, 2), dtype=torch.int32, device=dev) for _ in range(2)]
+    out = torch.empty(n, device=dev)
+    pb = (ctypes.c_void_p * 2)(*[b.data_ptr() for b in bufs])
+    pf = (ctypes.c_void_p * 2)(*[f.data_ptr() for f in flags])
+    before = ctypes.c_int(-1)
+    _lib.check(lib.ffi_wait_timeouts(ctypes.byref(before)))
+    _lib.check(lib.ffi_set_wait_limit_ticks(2_000_000))  # about a millisecond
+    try:
+        t0 = time.perf_counter()
+        _lib.check(lib.ffi_peer_sum(pb, pf, 0, 2, n, 1, out.data_ptr(), torch.cuda.current_stream(dev).cuda_stream))
+        torch.cuda.synchronize()
+        assert time.perf_counter() - t0 < 1.0
+    finally:
+        _lib.check(lib.ffi_set_wait_limit_ticks(4_000_000_000))
+    after = ctypes.c_int(-1)
+    _lib.check(lib.ffi_wait_timeouts(ctypes.byref(after)))
+    assert after.value > before.value
+    cases.EXPECTED_WAIT_TIMEOUTS += after.value - before.value
+    # the context is still usable and rank 0's own flag went up
+    assert int(flags[0][1, 0]) == 1 and int(flags[1][1, 0]) == 1
+    assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0
+    assert lib.ffi_set_wait_limit_ticks(5) == 1
 
 
 def _torch_reference(xT, idx, W, g, chunk=4096):

@@ -103,4 +103,5 @@ def test_no_device_wait_gave_up(cuda_device):
     assert torch.allclose(gw, ref_gw, rtol=1e-4, atol=1e-4)
     count = ctypes.c_int(-1)
     _lib.check(_lib.load().ffi_wait_timeouts(ctypes.byref(count)))
-    assert count.value == 0
+    import cases
+    assert count.value == cases.EXPECTED_WAIT_TIMEOUTS  # only the waits a test made run out on purpose
