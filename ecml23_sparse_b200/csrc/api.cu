@@ -59,6 +59,20 @@ int check_plan_device(const ffi_plan* plan) {
     return FFI_OK;
 }
 
+struct Bf16LossEpilogue {
+    float* gT;
+    long long ldg;
+    float scale;
+    double* loss_partials;
+    int loss_kind;
+    int* ctas;
+};
+int launch_forward_bf16(const void* xT, int64_t ldx, const int32_t* idx, const void* W, const float* bias, float* y,
+                        int64_t B, int64_t N, int64_t L, int64_t K, const Bf16LossEpilogue* loss, cudaStream_t stream,
+                        bool* handled);
+int forward_bf16_warps(int64_t B, int64_t N, int64_t K, bool loss_epilogue);
+int launch_transpose_pad_bf16(const void* src, void* dst, int rows, int cols, int64_t ld_dst, cudaStream_t stream);
+
 bool forward_uses_smem_x(int B, int N, int K, int* bpl_out);
 int launch_widen_bf16(const void* src, float* dst, int64_t n, cudaStream_t stream);
 bool grad_w_uses_smem_x(int B, int N, int K, int* bpl_out);
@@ -144,6 +158,49 @@ int widen_inputs(const void* x, const void* W, int64_t B, int64_t N, int64_t L, 
     return FFI_OK;
 }
 
+// bf16 storage goes to the tiled forward kernel natively where the fp32 dispatch would take that kernel too
+// (x too wide for shared memory, or K not a multiple of 4).
+bool bf16_takes_tiled_forward(int64_t B, int64_t N, int64_t K) {
+    return K % 4 != 0 || !forward_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
+}
+
+// stage_x for bf16 elements (esize 2): the same [N][ld] layouts, half the bytes.
+int stage_x_any(const XPlan& xp, const void* x, void* ws, int64_t B, int64_t N, int x_transposed, size_t esize,
+                cudaStream_t stream, const void** xT) {
+    if (!xp.copy) {
+        *xT = x;
+        return FFI_OK;
+    }
+    if (x_transposed) {
+        if (xp.ld != B) FFI_CUDA_CHECK(cudaMemsetAsync(ws, 0, static_cast<size_t>(N) * xp.ld * esize, stream));
+        FFI_CUDA_CHECK(cudaMemcpy2DAsync(ws, xp.ld * esize, x, B * esize, B * esize, N, cudaMemcpyDeviceToDevice, stream));
+    } else {
+        const int rc = launch_transpose_pad_bf16(x, ws, static_cast<int>(B), static_cast<int>(N), xp.ld, stream);
+        if (rc != FFI_OK) return rc;
+    }
+    *xT = ws;
+    return FFI_OK;
+}
+
+// bf16 x as [N][ld]: used in place when it already is transposed, else transposed into the workspace.
+int stage_x_bf16(const void* x, void* workspace, size_t workspace_bytes, int64_t B, int64_t N, int x_transposed,
+                 cudaStream_t stream, const void** xT, int64_t* ldx) {
+    if (x_transposed) {
+        *xT = x;
+        *ldx = B;
+        return FFI_OK;
+    }
+    const int64_t ld = round_up(B, 128);
+    const size_t need = static_cast<size_t>(N) * ld * 2;
+    if (!workspace || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 16 != 0)
+        return fail(FFI_ERR_WORKSPACE, "bf16 x given as [B,N] needs %zu bytes of 16-byte aligned workspace", need);
+    const int rc = launch_transpose_pad_bf16(x, workspace, static_cast<int>(B), static_cast<int>(N), ld, stream);
+    if (rc != FFI_OK) return rc;
+    *xT = workspace;
+    *ldx = ld;
+    return FFI_OK;
+}
+
 }  // namespace
 }  // namespace ffi
 
@@ -168,6 +225,39 @@ extern "C" int ffi_forward(const void* x, const int32_t* idx, const void* W, con
     if (rc != FFI_OK) return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     if (dtype == FFI_BF16) {
+        // native bf16 kernel (x tile and W rows stay bf16 in shared memory) where the shape allows it
+        if (forward_bf16_warps(B, N, K, false) >= 4) {
+            const void* xT = nullptr;
+            int64_t ldx = 0;
+            rc = stage_x_bf16(x, workspace, workspace_bytes, B, N, x_transposed, stream, &xT, &ldx);
+            if (rc != FFI_OK) return rc;
+            bool handled = false;
+            rc = launch_forward_bf16(xT, ldx, idx, W, bias, y, B, N, L, K, nullptr, stream, &handled);
+            if (rc != FFI_OK || handled) return rc;
+        }
+        // wide inputs / odd fan-in: the tiled kernel reads bf16 x and W itself
+        if (bf16_takes_tiled_forward(B, N, K)) {
+            const XPlan xpb = plan_x(forward_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr),
+                                     B, N, x_transposed);
+            if (xpb.copy && (!workspace || workspace_bytes < xpb.bytes || reinterpret_cast<uintptr_t>(workspace) % 16 != 0))
+                return fail(FFI_ERR_WORKSPACE, "ffi_forward needs %zu bytes of 16-byte aligned workspace, got %zu",
+                            xpb.bytes, workspace_bytes);
+            FwdArgs ab;
+            rc = stage_x_any(xpb, x, workspace, B, N, x_transposed, 2, stream, &ab.xT);
+            if (rc != FFI_OK) return rc;
+            ab.ldx = xpb.ld;
+            ab.idx = idx;
+            ab.W = W;
+            ab.bf16 = true;
+            ab.bias = bias;
+            ab.y = y;
+            ab.B = static_cast<int>(B);
+            ab.N = static_cast<int>(N);
+            ab.L = static_cast<int>(L);
+            ab.K = static_cast<int>(K);
+            return launch_forward(ab, stream);
+        }
+        // otherwise both are widened (exactly) into the workspace and the fp32 kernels run
         const float *x32 = nullptr, *W32 = nullptr;
         void* rest = nullptr;
         size_t rest_bytes = 0;
@@ -239,17 +329,28 @@ static int backward_impl(const void* x, const int32_t* idx, const void* W, const
     if (!x || !idx || !W || (!g && !gT_in)) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_backward");
     int rc = check_shape(B, N, L, K);
     if (rc != FFI_OK) return rc;
+    if (dtype != FFI_F32 && dtype != FFI_BF16) return fail(FFI_ERR_UNSUPPORTED, "ffi_backward: dtype %d not supported", dtype);
+    // bf16 storage: the group kernel (one pass, batch <= 128) and the kernels for wide inputs read bf16 x and W
+    // themselves; for the other shapes both are widened (exactly) into the workspace and the fp32 kernels run.
+    bool bf16 = false;
     if (dtype == FFI_BF16) {
-        const float *x32 = nullptr, *W32 = nullptr;
-        void* rest = nullptr;
-        size_t rest_bytes = 0;
-        rc = widen_inputs(x, W, B, N, L, K, workspace, workspace_bytes, static_cast<cudaStream_t>(stream_v), &x32, &W32,
-                          &rest, &rest_bytes);
-        if (rc != FFI_OK) return rc;
-        return backward_impl(x32, idx, W32, g, gT_in, ldg_in, plan, grad_x, grad_w, grad_bias, B, N, L, K, x_transposed,
-                             FFI_F32, rest, rest_bytes, stream_v);
+        const bool one_pass = grad_x && grad_w && plan && backward_fused_takes_bf16(plan, B);
+        const bool w_native = !(grad_w || grad_bias) ||
+                              !grad_w_stream_applicable(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), idx);
+        const bool x_native = !grad_x || (plan && !plan->has_chunks);
+        bf16 = one_pass || (w_native && x_native && !(grad_x && grad_w && plan && backward_fused_applicable(plan, B)));
+        if (!bf16) {
+            const float *x32 = nullptr, *W32 = nullptr;
+            void* rest = nullptr;
+            size_t rest_bytes = 0;
+            rc = widen_inputs(x, W, B, N, L, K, workspace, workspace_bytes, static_cast<cudaStream_t>(stream_v), &x32,
+                              &W32, &rest, &rest_bytes);
+            if (rc != FFI_OK) return rc;
+            return backward_impl(x32, idx, W32, g, gT_in, ldg_in, plan, grad_x, grad_w, grad_bias, B, N, L, K,
+                                 x_transposed, FFI_F32, rest, rest_bytes, stream_v);
+        }
     }
-    if (dtype != FFI_F32) return fail(FFI_ERR_UNSUPPORTED, "ffi_backward: dtype %d not supported", dtype);
+    const size_t esize = bf16 ? 2 : 4;
     if (grad_x) {
         if (!plan) return fail(FFI_ERR_INVALID_ARGUMENT, "grad_x needs a plan (ffi_plan_create)");
         if (plan->L != L || plan->K != K || plan->N != N)
@@ -304,7 +405,8 @@ static int backward_impl(const void* x, const int32_t* idx, const void* W, const
 
     GradXArgs ax;
     ax.idx = idx;
-    ax.W = static_cast<const float*>(W);
+    ax.W = W;
+    ax.w_bf16 = bf16;
     ax.g = g;
     ax.gT = gT;
     ax.ldg = ldg;
@@ -317,16 +419,17 @@ static int backward_impl(const void* x, const int32_t* idx, const void* W, const
     ax.K = Ki;
 
     if (fused) {
-        const float* xT = static_cast<const float*>(x);
+        const void* xT = x;
         int64_t ldx = B;
         if (!x_transposed) {
             ldx = round_up(B, 128);
             void* dst = nullptr;
-            rc = take(static_cast<size_t>(N) * ldx * 4, "the transposed x", &dst);
+            rc = take(static_cast<size_t>(N) * ldx * esize, "the transposed x", &dst);
             if (rc != FFI_OK) return rc;
-            rc = launch_transpose_pad(static_cast<const float*>(x), static_cast<float*>(dst), Bi, Ni, ldx, stream);
+            rc = bf16 ? launch_transpose_pad_bf16(x, dst, Bi, Ni, ldx, stream)
+                      : launch_transpose_pad(static_cast<const float*>(x), static_cast<float*>(dst), Bi, Ni, ldx, stream);
             if (rc != FFI_OK) return rc;
-            xT = static_cast<const float*>(dst);
+            xT = dst;
         }
         void* part = nullptr;
         rc = take(backward_fused_workspace_bytes(plan, B), "the grad_x partial sums", &part);
@@ -344,11 +447,18 @@ static int backward_impl(const void* x, const int32_t* idx, const void* W, const
             rc = take(xp.bytes, "x", &xdst);
             if (rc != FFI_OK) return rc;
         }
-        const float* xT = nullptr;
-        rc = stage_x(xp, static_cast<const float*>(x), static_cast<float*>(xdst), B, N, x_transposed, stream, &xT);
+        const void* xT = nullptr;
+        if (bf16) {
+            rc = stage_x_any(xp, x, xdst, B, N, x_transposed, 2, stream, &xT);
+        } else {
+            const float* xf = nullptr;
+            rc = stage_x(xp, static_cast<const float*>(x), static_cast<float*>(xdst), B, N, x_transposed, stream, &xf);
+            xT = xf;
+        }
         if (rc != FFI_OK) return rc;
         GradWArgs a;
         a.xT = xT;
+        a.bf16 = bf16;
         a.ldx = xp.ld;
         a.idx = idx;
         a.g = g;
@@ -399,10 +509,10 @@ int launch_forward_loss_tile(const FwdArgs& a, float* gT, int64_t ldg, float sca
 size_t forward_topk_workspace_bytes(int64_t B);
 int launch_forward_topk_stream(const FwdArgs& a, void* scratch, float* top_val, int* top_idx, int kk, int label_offset,
                                cudaStream_t stream, bool* handled);
-int launch_bce_positive_fix(const float* xT, int64_t ldx, const int* idx, const float* W, const float* bias,
+int launch_bce_positive_fix(const void* xT, int64_t ldx, const int* idx, const void* W, const float* bias,
                             const int* row_ptr, const int* labels, float* gT, int64_t ldg, float* loss,
                             const double* partials, int nPartials, double* pos_partials, float scale, int B,
-                            int64_t L, int K, int64_t label_offset, int loss_kind, cudaStream_t stream);
+                            int64_t L, int K, int64_t label_offset, int loss_kind, bool bf16, cudaStream_t stream);
 constexpr size_t kBcePartialBytes = 1024 * sizeof(double);  // >= one partial per CTA of the forward kernel
 }  // namespace ffi
 
@@ -422,7 +532,8 @@ extern "C" int ffi_forward_loss(int loss_kind, const void* x, const int32_t* idx
         return fail(FFI_ERR_UNSUPPORTED, "unknown loss kind %d", loss_kind);
     int rc = check_shape(B, N, L, K);
     if (rc != FFI_OK) return rc;
-    if (dtype != FFI_F32) return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_loss: dtype %d not supported", dtype);
+    if (dtype != FFI_F32 && dtype != FFI_BF16)
+        return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_loss: dtype %d not supported", dtype);
     if (L_total < L) return fail(FFI_ERR_INVALID_ARGUMENT, "L_total must be >= L");
     if (reinterpret_cast<uintptr_t>(gT) % 16 != 0) return fail(FFI_ERR_INVALID_ARGUMENT, "gT must be 16-byte aligned");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
@@ -431,9 +542,63 @@ extern "C" int ffi_forward_loss(int loss_kind, const void* x, const int32_t* idx
         return fail(FFI_ERR_WORKSPACE, "ffi_forward_loss needs %zu bytes of %zu-byte aligned workspace",
                     ffi_forward_bce_workspace_bytes(B, N, L, K, x_transposed, dtype), kAlign);
     unsigned char* ws = static_cast<unsigned char*>(workspace);
+    const bool bf16_tiled = dtype == FFI_BF16 && forward_bf16_warps(B, N, K, true) < 4 && bf16_takes_tiled_forward(B, N, K);
+    if (dtype == FFI_BF16 && forward_bf16_warps(B, N, K, true) < 4 && !bf16_tiled) {
+        // no native kernel for this shape: x and W are widened (exactly) at the front of the workspace
+        const float *x32 = nullptr, *W32 = nullptr;
+        void* rest = nullptr;
+        size_t rest_bytes = 0;
+        rc = widen_inputs(x, W, B, N, L, K, workspace, workspace_bytes, stream, &x32, &W32, &rest, &rest_bytes);
+        if (rc != FFI_OK) return rc;
+        return ffi_forward_loss(loss_kind, x32, idx, W32, bias, row_ptr, labels, gT, loss, B, N, L, K, L_total,
+                                label_offset, x_transposed, FFI_F32, rest, rest_bytes, stream_v);
+    }
     double* partials = reinterpret_cast<double*>(ws);
     double* pos_partials = reinterpret_cast<double*>(ws + align_up(kBcePartialBytes));
     float* xws = reinterpret_cast<float*>(ws + align_up(kBcePartialBytes) + align_up(static_cast<size_t>(B) * sizeof(double)));
+    const float scale = static_cast<float>(1.0 / (static_cast<double>(B) * static_cast<double>(L_total)));
+    const int64_t ldg = transposed_g_stride(B);
+    if (bf16_tiled) {
+        const XPlan xpb = plan_x(forward_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr),
+                                 B, N, x_transposed);
+        FwdArgs ab;
+        rc = stage_x_any(xpb, x, xws, B, N, x_transposed, 2, stream, &ab.xT);
+        if (rc != FFI_OK) return rc;
+        ab.ldx = xpb.ld;
+        ab.idx = idx;
+        ab.W = W;
+        ab.bf16 = true;
+        ab.bias = bias;
+        ab.y = nullptr;
+        ab.B = static_cast<int>(B);
+        ab.N = static_cast<int>(N);
+        ab.L = static_cast<int>(L);
+        ab.K = static_cast<int>(K);
+        int ctas_t = 0;
+        rc = launch_forward_loss_tile(ab, gT, ldg, scale, partials, &ctas_t, loss_kind, stream);
+        if (rc != FFI_OK) return rc;
+        return launch_bce_positive_fix(ab.xT, xpb.ld, idx, W, bias, row_ptr, labels, gT, ldg, loss, partials, ctas_t,
+                                       pos_partials, scale, static_cast<int>(B), L, static_cast<int>(K), label_offset,
+                                       loss_kind, true, stream);
+    }
+    if (dtype == FFI_BF16) {
+        const size_t used = reinterpret_cast<unsigned char*>(xws) - ws;
+        const void* xTb = nullptr;
+        int64_t ldxb = 0;
+        rc = stage_x_bf16(x, xws, workspace_bytes - used, B, N, x_transposed, stream, &xTb, &ldxb);
+        if (rc != FFI_OK) return rc;
+        int ctas_b = 0;
+        bool handled_b = false;
+        Bf16LossEpilogue e{gT, ldg, scale, partials, loss_kind, &ctas_b};
+        rc = launch_forward_bf16(xTb, ldxb, idx, W, bias, nullptr, B, N, L, K, &e, stream, &handled_b);
+        if (rc != FFI_OK) return rc;
+        if (!handled_b) return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_loss: unaligned bf16 W or idx");
+        if (static_cast<size_t>(ctas_b) * sizeof(double) > kBcePartialBytes)
+            return fail(FFI_ERR_UNSUPPORTED, "too many loss partials (%d)", ctas_b);
+        return launch_bce_positive_fix(xTb, ldxb, idx, W, bias, row_ptr, labels, gT, ldg, loss, partials, ctas_b,
+                                       pos_partials, scale, static_cast<int>(B), L, static_cast<int>(K), label_offset,
+                                       loss_kind, true, stream);
+    }
 
     const bool smem = forward_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
     const XPlan xp = plan_x(smem, B, N, x_transposed);
@@ -451,8 +616,6 @@ extern "C" int ffi_forward_loss(int loss_kind, const void* x, const int32_t* idx
     a.N = static_cast<int>(N);
     a.L = static_cast<int>(L);
     a.K = static_cast<int>(K);
-    const float scale = static_cast<float>(1.0 / (static_cast<double>(B) * static_cast<double>(L_total)));
-    const int64_t ldg = transposed_g_stride(B);
     int ctas = 0;
     bool handled = false;
     rc = launch_forward_bce_stream(a, gT, ldg, scale, partials, &ctas, loss_kind, stream, &handled);
@@ -465,7 +628,7 @@ extern "C" int ffi_forward_loss(int loss_kind, const void* x, const int32_t* idx
         return fail(FFI_ERR_UNSUPPORTED, "too many loss partials (%d)", ctas);
     return launch_bce_positive_fix(xT, xp.ld, idx, a.W, bias, row_ptr, labels, gT, ldg, loss, partials, ctas,
                                    pos_partials, scale, static_cast<int>(B), L, static_cast<int>(K), label_offset, loss_kind,
-                                   stream);
+                                   false, stream);
 }
 
 extern "C" size_t ffi_forward_topk_workspace_bytes(int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed,

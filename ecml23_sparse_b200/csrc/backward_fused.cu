@@ -24,6 +24,8 @@
 // No atomics on floating-point data: results are bit-reproducible.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "ffi_common.cuh"
 
 namespace ffi {
@@ -118,10 +120,10 @@ __device__ __forceinline__ void store_zero_vec(float* dst) {
 }
 
 struct BwdFusedParams {
-    const float* W;
+    const void* W;   // fp32; the group kernel also takes bf16 (its TX)
     const float* gT;
     long long ldg;
-    const float* xT;
+    const void* xT;  // same element type as W
     long long ldx;
     const int* cperm;
     const int* cptr;
@@ -172,7 +174,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_bwd_fused_kernel(BwdFusedPara
 #pragma unroll
         for (int q = 0; q < BPL; ++q) {
             const int b = lane * BPL + q;
-            xv[q] = (i < N && b < p.B) ? __ldg(p.xT + static_cast<size_t>(i) * p.ldx + b) : 0.f;
+            xv[q] = (i < N && b < p.B) ? __ldg(static_cast<const float*>(p.xT) + static_cast<size_t>(i) * p.ldx + b) : 0.f;
         }
         acc[j].zero();
         xr[j].set(xv);
@@ -207,7 +209,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_bwd_fused_kernel(BwdFusedPara
             for (int u = 0; u < kStageUnroll; ++u) {
                 if (pos[u] >= 0) {
                     uint2* d = dst + e0 + u * kThreads;
-                    __pipeline_memcpy_async(&d->x, p.W + pos[u], 4);
+                    __pipeline_memcpy_async(&d->x, static_cast<const float*>(p.W) + pos[u], 4);
                     const int rel = pos[u] - pos0;
                     const int ol = p.kShift >= 0 ? (rel >> p.kShift) : rel / K;
                     const int k = rel - ol * K;
@@ -513,9 +515,17 @@ __device__ __forceinline__ void tmem_store_sums(unsigned taddr, const Lane8& sum
 // so a warp step works on G consecutive entries of a run.  G = 2 is the batch 65..128 case described above;
 // G = 4 covers batch <= 64 with a quarter of a warp per entry (a quarter warp reads one 128-byte half of a
 // tile row per LDS.128: conflict-free), which halves the shared-memory traffic per entry once more.
-template <int NI, int THREADS, int SLOTS, int G>
+//
+// TX is the storage type of x and W.  bf16 x is widened (exactly) on its way into tensor memory.  A bf16
+// weight is fetched as the aligned 4-byte word that holds it (cp.async copies at least 4 bytes) and turned
+// into its fp32 bit pattern by the thread that fetched it once the copy has landed (the entry's code tells
+// which half: the chunk's first position is even, so the parity of the position within the chunk is the
+// parity of the flat position).
+template <int NI, int THREADS, int SLOTS, int G, typename TX>
 __global__ void __launch_bounds__(THREADS, 1)
     ffi_bwd_pairs_kernel(BwdFusedParams p, const __grid_constant__ CUtensorMap g_map) {
+    constexpr bool kBf16 = !std::is_same<TX, float>::value;
+    const TX* xTt = static_cast<const TX*>(p.xT);
     constexpr int LG = 32 / G;    // lanes per group
     constexpr int BT = 8 * LG;    // batch columns of the tile
     constexpr int HALF = 2 * BT;  // bytes between a lane's two 16-byte pieces of a tile row
@@ -562,7 +572,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
         for (int m = 0; m < 8; ++m) {
             const int b = (m < 4 ? 0 : BT / 2) + 4 * q + (m & 3);
-            xv[m] = __float_as_uint((i < N && b < p.B) ? __ldg(p.xT + static_cast<size_t>(i) * p.ldx + b) : 0.f);
+            xv[m] = __float_as_uint((i < N && b < p.B) ? widen(xTt[static_cast<size_t>(i) * p.ldx + b]) : 0.f);
             zero[m] = 0u;
         }
         tmem_store8(taddr0 + j * 16, zero);
@@ -593,10 +603,21 @@ __global__ void __launch_bounds__(THREADS, 1)
         if (tid < CPN) cpv = __ldg(p.cptr + c * (N + 1) + min(i_lo + tid, i_hi)) - e_lo;
     };
     auto emit_one = [&](uint2* d, int ps, int pos0) {
-        __pipeline_memcpy_async(&d->x, p.W + ps, 4);
+        if constexpr (kBf16) __pipeline_memcpy_async(&d->x, static_cast<const unsigned*>(p.W) + (ps >> 1), 4);
+        else __pipeline_memcpy_async(&d->x, static_cast<const float*>(p.W) + ps, 4);
         const int rel = ps - pos0;
         const int ol = p.kShift >= 0 ? (rel >> p.kShift) : rel / K;
         d->y = static_cast<unsigned>(ol * (BT * 4)) | (static_cast<unsigned>(rel) << kKShift);
+    };
+    // bf16 weights: the words this thread fetched for buffer `buf` (cnt entries) become fp32 bit patterns
+    auto widen_staged = [&](int buf, int cnt) {
+        if constexpr (kBf16) {
+            uint2* dst = ent_s + buf * p.entCap;
+            for (int e = tid; e < cnt; e += kThreads) {
+                const uint2 en = dst[e];
+                dst[e].x = ((en.y >> kKShift) & 1u) ? (en.x & 0xffff0000u) : (en.x << 16);
+            }
+        }
     };
     auto emit = [&](long long c, int buf, int e_lo, int cnt) {
         const int pos0 = static_cast<int>(c * T) * K;
@@ -612,10 +633,12 @@ __global__ void __launch_bounds__(THREADS, 1)
 
     int pl_lo = 0, pl_cnt = 0;  // bounds of the chunk whose positions the registers hold
     int nb_lo = 0, nb_cnt = 0;  // bounds of the chunk after that
+    int first_cnt = 0;
     if (c_begin < c_end) {
         slice_bounds(c_begin, pl_lo, pl_cnt);
         load_pos(c_begin, pl_lo, pl_cnt);
         emit(c_begin, 0, pl_lo, pl_cnt);
+        first_cnt = pl_cnt;
         if (c_begin + 1 < c_end) {
             slice_bounds(c_begin + 1, pl_lo, pl_cnt);
             load_pos(c_begin + 1, pl_lo, pl_cnt);
@@ -624,6 +647,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
     __pipeline_commit();
     __pipeline_wait_prior(0);
+    widen_staged(0, first_cnt);
     float* dbuf = dbuf_s + warp * (kSlots * kDRow);
     float* dlane = dbuf + lane;                                   // this lane's column of the dot buffer
     const int dcode_delta = 32 + grp - lane;                      // from a lane's dot to its entry's code
@@ -657,6 +681,7 @@ __global__ void __launch_bounds__(THREADS, 1)
             tma_load_2d(g_s, &g_map, 0, static_cast<int>(o0), g_bar);
         }
         pending = c;
+        const int staged_cnt = c + 1 < c_end ? pl_cnt : 0;  // entries of chunk c + 1 going into the other buffer
         if (c + 1 < c_end) emit(c + 1, buf ^ 1, pl_lo, pl_cnt);
         __pipeline_commit();
         if (c + 2 < c_end) {
@@ -768,6 +793,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         tmem_wait_store();
 
         __pipeline_wait_prior(0);  // this thread's staged weights of the next chunk are in place
+        widen_staged(buf ^ 1, staged_cnt);
 
         // Every segChunks chunks the running grad_x sums go out as one partial and restart from zero.
         const long long done = c - c_begin + 1;
@@ -909,6 +935,14 @@ bool backward_fused_applicable(const ffi_plan* plan, int64_t B) {
     return fused_config(plan, B, dev, &c);
 }
 
+// True when the one-pass backward of this shape is the group kernel, which also reads bf16 x and W.
+bool backward_fused_takes_bf16(const ffi_plan* plan, int64_t B) {
+    DeviceInfo dev;
+    if (get_device_info(&dev) != FFI_OK) return false;
+    FusedConfig c;
+    return fused_config(plan, B, dev, &c) && c.groups != 0;
+}
+
 size_t backward_fused_workspace_bytes(const ffi_plan* plan, int64_t B) {
     DeviceInfo dev;
     if (get_device_info(&dev) != FFI_OK) return 0;
@@ -922,7 +956,7 @@ int reduce_range_partials(const float* partial, float* gx, int R, int N, int B, 
 
 // grad_x (always), grad_W (when gW != nullptr) and grad_bias (when gbias != nullptr, from gT) in one
 // kernel (grad_bias by a separate pass over gT where the pair kernel does not apply).  xT is x as [N][ldx].
-int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, float* gW, float* gbias,
+int launch_backward_fused(const GradXArgs& a, const void* xT, int64_t ldx, float* gW, float* gbias,
                           cudaStream_t stream) {
     DeviceInfo dev;
     int rc = get_device_info(&dev);
@@ -962,6 +996,7 @@ int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, floa
     p.segChunks = c.segChunks;
     p.S = c.S;
     const bool pairs = c.groups != 0;
+    if (a.w_bf16 && !pairs) return fail(FFI_ERR_UNSUPPORTED, "this fused backward kernel reads fp32 x and W");
     if (gbias && !pairs) {  // the other kernels leave grad_bias to a pass over gT
         rc = launch_bias_grad_rows(a.gT, a.ldg, a.L, gbias, stream);
         if (rc != FFI_OK) return rc;
@@ -973,15 +1008,16 @@ int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, floa
         rc = encode_g_map(&g_map, a.gT, a.L, a.ldg, a.plan->chunk_rows, c.Bpad);
         if (rc != FFI_OK) return rc;
         dim3 grid(static_cast<unsigned>(c.R), static_cast<unsigned>(c.iparts), 1);
-        if (c.groups == 2) {
-            auto kern = ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 16, 2>;
+        auto launch_group = [&](auto kern) -> int {
             FFI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(c.smem)));
             kern<<<grid, kGroupThreads, c.smem, stream>>>(p, g_map);
-        } else {
-            auto kern = ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 8, 4>;
-            FFI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(c.smem)));
-            kern<<<grid, kGroupThreads, c.smem, stream>>>(p, g_map);
-        }
+            return FFI_OK;
+        };
+        if (c.groups == 2 && !a.w_bf16) rc = launch_group(ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 16, 2, float>);
+        else if (c.groups == 2) rc = launch_group(ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 16, 2, __nv_bfloat16>);
+        else if (!a.w_bf16) rc = launch_group(ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 8, 4, float>);
+        else rc = launch_group(ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 8, 4, __nv_bfloat16>);
+        if (rc != FFI_OK) return rc;
         FFI_LAUNCH_CHECK("ffi_bwd_pairs_kernel");
         rc = FFI_OK;
     }

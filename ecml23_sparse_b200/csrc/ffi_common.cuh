@@ -65,13 +65,39 @@ __device__ __forceinline__ float vec_get(const float4& v, int j) {
     return j == 0 ? v.x : (j == 1 ? v.y : (j == 2 ? v.z : v.w));
 }
 
+// ---- storage types of x and W: fp32 or bf16 (a bf16 value widens to fp32 exactly) ----------------
+__device__ __forceinline__ float widen(float v) { return v; }
+__device__ __forceinline__ float widen(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float bf16_lo(unsigned word) { return __uint_as_float(word << 16); }
+__device__ __forceinline__ float bf16_hi(unsigned word) { return __uint_as_float(word & 0xffff0000u); }
+
+// The BPL consecutive batch elements a lane holds, loaded from `base` (element type T) at vector index `v`.
+template <int BPL>
+__device__ __forceinline__ typename Vec<BPL>::type load_lane_vec(const float* base, size_t v) {
+    return __ldg(reinterpret_cast<const typename Vec<BPL>::type*>(base) + v);
+}
+template <int BPL>
+__device__ __forceinline__ typename Vec<BPL>::type load_lane_vec(const __nv_bfloat16* base, size_t v) {
+    if constexpr (BPL == 4) {
+        const uint2 r = __ldg(reinterpret_cast<const uint2*>(base) + v);
+        return make_float4(bf16_lo(r.x), bf16_hi(r.x), bf16_lo(r.y), bf16_hi(r.y));
+    } else if constexpr (BPL == 2) {
+        const unsigned r = __ldg(reinterpret_cast<const unsigned*>(base) + v);
+        return make_float2(bf16_lo(r), bf16_hi(r));
+    } else {
+        return __bfloat162float(base[v]);
+    }
+}
+
 // ---- launchers implemented in the .cu files ---------------------------------------
-// xT is x in [N][ldx] layout (batch contiguous), fp32.
+// xT is x in [N][ldx] layout (batch contiguous); xT and W are fp32, or bf16 when `bf16` is set (only the
+// tiled kernels take bf16; the callers see to that).
 struct FwdArgs {
-    const float* xT;
+    const void* xT;
     int64_t ldx;
     const int32_t* idx;
-    const float* W;
+    const void* W;
+    bool bf16 = false;
     const float* bias;
     float* y;
     int B, N, L, K;
@@ -79,7 +105,8 @@ struct FwdArgs {
 int launch_forward(const FwdArgs& a, cudaStream_t stream);
 
 struct GradWArgs {
-    const float* xT;
+    const void* xT;  // fp32, or bf16 when `bf16` is set (tiled kernel only)
+    bool bf16 = false;
     int64_t ldx;
     const int32_t* idx;
     const float* g;
@@ -132,7 +159,8 @@ int check_plan_device(const ffi_plan* plan);
 
 struct GradXArgs {
     const int32_t* idx;
-    const float* W;
+    const void* W;       // fp32, or bf16 when w_bf16 is set (the wide-input kernel and the group kernel take bf16)
+    bool w_bf16 = false;
     const float* g;
     const float* gT;  // as in GradWArgs; required by the narrow-input kernel
     int64_t ldg;
@@ -151,7 +179,9 @@ int launch_grad_x(const GradXArgs& a, cudaStream_t stream);
 // grad_x and grad_W in one pass over the transposed index (narrow inputs, batch <= 128).
 bool backward_fused_applicable(const ffi_plan* plan, int64_t B);
 size_t backward_fused_workspace_bytes(const ffi_plan* plan, int64_t B);
-int launch_backward_fused(const GradXArgs& a, const float* xT, int64_t ldx, float* gW, float* gbias,
+bool backward_fused_takes_bf16(const ffi_plan* plan, int64_t B);
+// xT (x as [N][ldx]) has the element type of a.W: fp32, or bf16 when a.w_bf16 is set.
+int launch_backward_fused(const GradXArgs& a, const void* xT, int64_t ldx, float* gW, float* gbias,
                           cudaStream_t stream);
 
 }  // namespace ffi

@@ -15,6 +15,8 @@
 //     along o (128 B per warp store) instead of striding by L.
 // The kernel is persistent: gridDim.x CTAs per batch tile loop over the output tiles.
 // When x_s does not fit (wide N), the same code gathers x from global memory (L2).
+#include <type_traits>
+
 #include "ffi_common.cuh"
 
 namespace ffi {
@@ -24,10 +26,10 @@ constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
 
 struct FwdKernelParams {
-    const float* xT;
+    const void* xT;  // element type TX of the kernel: float or __nv_bfloat16
     long long ldx;
     const int* idx;
-    const float* W;
+    const void* W;   // same element type
     const float* bias;
     float* y;
     int B, N, L, K;
@@ -59,9 +61,15 @@ __device__ __forceinline__ void loss_for_negative(int kind, float z, float& valu
     }
 }
 
-template <int BPL, bool XSMEM, bool LOSS>
+// TX: storage type of x and W.  bf16 values are widened where they are loaded (the x tile and the staged W
+// rows in shared memory are fp32; x gathered from global memory is widened in registers), so the
+// arithmetic is that of the fp32 kernel on exactly the same values, at half the gather traffic.
+template <int BPL, bool XSMEM, bool LOSS, typename TX>
 __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_kernel(FwdKernelParams p) {
     constexpr int BT = 32 * BPL;
+    constexpr bool kBf16 = !std::is_same<TX, float>::value;
+    const TX* xT = static_cast<const TX*>(p.xT);
+    const TX* Wt = static_cast<const TX*>(p.W);
     using V = typename Vec<BPL>::type;
     extern __shared__ __align__(16) unsigned char smem_raw[];
 
@@ -90,7 +98,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_kernel(FwdKernelParams p)
             int i = e / BT;
             int bl = e - i * BT;
             int b = b0 + bl;
-            float v = b < p.B ? p.xT[static_cast<size_t>(i) * p.ldx + b] : 0.f;
+            float v = b < p.B ? widen(xT[static_cast<size_t>(i) * p.ldx + b]) : 0.f;
             x_s[i * BT + (bl & 31) * BPL + (bl >> 5)] = v;
         }
     }
@@ -101,12 +109,17 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_kernel(FwdKernelParams p)
         const int nrows = min(TO, static_cast<int>(L - o0));
         float* wd = w_s + buf * tileElems;
         int* id = i_s + buf * tileElems;
-        const float* wsrc = p.W + o0 * K;
+        const TX* wsrc = Wt + o0 * K;
         const int* isrc = p.idx + o0 * K;
         if (p.vec16) {
             const int nvec = nrows * K / 4;
             for (int v = tid; v < nvec; v += kThreads) {
-                __pipeline_memcpy_async(wd + 4 * v, wsrc + 4 * v, 16);
+                if constexpr (kBf16) {  // a widening copy: four bf16 weights -> four fp32 words
+                    const uint2 r = __ldg(reinterpret_cast<const uint2*>(wsrc) + v);
+                    *reinterpret_cast<float4*>(wd + 4 * v) = make_float4(bf16_lo(r.x), bf16_hi(r.x), bf16_lo(r.y), bf16_hi(r.y));
+                } else {
+                    __pipeline_memcpy_async(wd + 4 * v, wsrc + 4 * v, 16);
+                }
                 __pipeline_memcpy_async(id + 4 * v, isrc + 4 * v, 16);
             }
         } else {
@@ -114,7 +127,8 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_kernel(FwdKernelParams p)
             for (int e = tid; e < n; e += kThreads) {
                 int r = e / K;
                 int k = e - r * K;
-                __pipeline_memcpy_async(wd + r * Kp + k, wsrc + e, 4);
+                if constexpr (kBf16) wd[r * Kp + k] = widen(wsrc[e]);
+                else __pipeline_memcpy_async(wd + r * Kp + k, wsrc + e, 4);
                 __pipeline_memcpy_async(id + r * Kp + k, isrc + e, 4);
             }
         }
@@ -122,7 +136,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_kernel(FwdKernelParams p)
     };
 
     const V* xs_lane = reinterpret_cast<const V*>(x_s) + lane;
-    const V* xg_lane = reinterpret_cast<const V*>(p.xT + b0) + lane;
+    const TX* xg_base = xT + b0;
     const size_t ldv = static_cast<size_t>(p.ldx / BPL);
 
     // Coalesced write-out of a finished tile: one warp per batch row, lanes along o.
@@ -159,7 +173,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_kernel(FwdKernelParams p)
 
     auto gather = [&](int i) -> V {
         if (XSMEM) return xs_lane[i * 32];
-        return __ldg(xg_lane + i * ldv);
+        return load_lane_vec<BPL>(xg_base, static_cast<size_t>(i) * ldv + lane);
     };
 
     int t = blockIdx.x;
@@ -281,10 +295,10 @@ int pick_TO(size_t budget, int N, int bpl, bool xsmem, int Kp) {
 
 constexpr int kMaxLossPartialsTile = 1024;  // doubles the caller's scratch holds for the per-CTA loss sums
 
-template <int BPL, bool XSMEM, bool LOSS>
+template <int BPL, bool XSMEM, bool LOSS, typename TX>
 int launch_fwd_t(const FwdKernelParams& p, size_t smem, int nBT, const DeviceInfo& dev,
                  cudaStream_t stream, int* ctas_out) {
-    auto kern = ffi_fwd_kernel<BPL, XSMEM, LOSS>;
+    auto kern = ffi_fwd_kernel<BPL, XSMEM, LOSS, TX>;
     FFI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(smem)));
     int occ = 0;
@@ -302,17 +316,17 @@ int launch_fwd_t(const FwdKernelParams& p, size_t smem, int nBT, const DeviceInf
     return FFI_OK;
 }
 
-template <bool LOSS>
+template <bool LOSS, typename TX>
 int launch_fwd_tile(const FwdKernelParams& p, size_t smem, int nBT, int bpl, bool xsmem, const DeviceInfo& dev,
                     cudaStream_t stream, int* ctas_out) {
     if (xsmem) {
-        if (bpl == 4) return launch_fwd_t<4, true, LOSS>(p, smem, nBT, dev, stream, ctas_out);
-        if (bpl == 2) return launch_fwd_t<2, true, LOSS>(p, smem, nBT, dev, stream, ctas_out);
-        return launch_fwd_t<1, true, LOSS>(p, smem, nBT, dev, stream, ctas_out);
+        if (bpl == 4) return launch_fwd_t<4, true, LOSS, TX>(p, smem, nBT, dev, stream, ctas_out);
+        if (bpl == 2) return launch_fwd_t<2, true, LOSS, TX>(p, smem, nBT, dev, stream, ctas_out);
+        return launch_fwd_t<1, true, LOSS, TX>(p, smem, nBT, dev, stream, ctas_out);
     }
-    if (bpl == 4) return launch_fwd_t<4, false, LOSS>(p, smem, nBT, dev, stream, ctas_out);
-    if (bpl == 2) return launch_fwd_t<2, false, LOSS>(p, smem, nBT, dev, stream, ctas_out);
-    return launch_fwd_t<1, false, LOSS>(p, smem, nBT, dev, stream, ctas_out);
+    if (bpl == 4) return launch_fwd_t<4, false, LOSS, TX>(p, smem, nBT, dev, stream, ctas_out);
+    if (bpl == 2) return launch_fwd_t<2, false, LOSS, TX>(p, smem, nBT, dev, stream, ctas_out);
+    return launch_fwd_t<1, false, LOSS, TX>(p, smem, nBT, dev, stream, ctas_out);
 }
 
 }  // namespace
@@ -363,7 +377,7 @@ static int launch_forward_tile(const FwdArgs& a, const TileLossEpilogue* loss, c
     p.L = a.L;
     p.K = a.K;
     p.Kp = static_cast<int>(round_up(a.K, 4));
-    p.vec16 = (a.K % 4 == 0) && (reinterpret_cast<uintptr_t>(a.W) % 16 == 0) &&
+    p.vec16 = (a.K % 4 == 0) && (reinterpret_cast<uintptr_t>(a.W) % (a.bf16 ? 8 : 16) == 0) &&
               (reinterpret_cast<uintptr_t>(a.idx) % 16 == 0);
     p.gT = loss ? loss->gT : nullptr;
     p.ldg = loss ? loss->ldg : 0;
@@ -384,12 +398,16 @@ static int launch_forward_tile(const FwdArgs& a, const TileLossEpilogue* loss, c
             reinterpret_cast<uintptr_t>(a.xT) % 16 != 0)
             return fail(FFI_ERR_INVALID_ARGUMENT, "wide-N forward needs a padded, aligned x copy");
     }
-    if (loss) return launch_fwd_tile<true>(p, smem, nBT, bpl, xsmem, dev, stream, loss->ctas);
-    return launch_fwd_tile<false>(p, smem, nBT, bpl, xsmem, dev, stream, nullptr);
+    if (a.bf16) {
+        if (loss) return launch_fwd_tile<true, __nv_bfloat16>(p, smem, nBT, bpl, xsmem, dev, stream, loss->ctas);
+        return launch_fwd_tile<false, __nv_bfloat16>(p, smem, nBT, bpl, xsmem, dev, stream, nullptr);
+    }
+    if (loss) return launch_fwd_tile<true, float>(p, smem, nBT, bpl, xsmem, dev, stream, loss->ctas);
+    return launch_fwd_tile<false, float>(p, smem, nBT, bpl, xsmem, dev, stream, nullptr);
 }
 
 int launch_forward(const FwdArgs& a, cudaStream_t stream) {
-    {
+    if (!a.bf16) {
         // Preferred: the barrier-free kernel (x tile in shared memory, K % 4 == 0, aligned rows).
         bool handled = false;
         int rc = launch_forward_stream(a, stream, &handled);

@@ -395,6 +395,7 @@ static int launch_forward_stream_impl(const FwdArgs& a, const BceEpilogue* bce, 
     DeviceInfo dev;
     int rc = get_device_info(&dev);
     if (rc != FFI_OK) return rc;
+    if (a.bf16) return FFI_OK;  // this kernel reads fp32 only
     if (a.K % 4 != 0 || reinterpret_cast<uintptr_t>(a.W) % 16 != 0 || reinterpret_cast<uintptr_t>(a.idx) % 16 != 0)
         return FFI_OK;
     int bpl = a.B <= 32 ? 1 : (a.B <= 64 ? 2 : 4);
@@ -406,10 +407,10 @@ static int launch_forward_stream_impl(const FwdArgs& a, const BceEpilogue* bce, 
     }
     if (bpl < 1) return FFI_OK;
     FwdStreamParams p;
-    p.xT = a.xT;
+    p.xT = static_cast<const float*>(a.xT);
     p.ldx = a.ldx;
     p.idx = a.idx;
-    p.W = a.W;
+    p.W = static_cast<const float*>(a.W);
     p.bias = a.bias;
     p.y = a.y;
     p.B = a.B;

@@ -24,7 +24,7 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kGRegs = 8;  // registers per thread that stage the next g tile
 
 struct GradWKernelParams {
-    const float* xT;
+    const void* xT;    // element type TX of the kernel: float or __nv_bfloat16
     long long ldx;
     const int* idx;
     const float* g;    // upstream gradient [B][L], or nullptr when gT is given
@@ -62,9 +62,12 @@ __device__ __forceinline__ void butterfly_reduce(float (&s)[G], int lane) {
     for (int off = 16 >> consumed; off >= 1; off /= 2) s[0] += __shfl_xor_sync(0xffffffffu, s[0], off);
 }
 
-template <int BPL, int G, bool XSMEM>
+// TX: storage type of x; bf16 values are widened where they are loaded (exactly), so the arithmetic is
+// that of the fp32 kernel on the same values.
+template <int BPL, int G, bool XSMEM, typename TX>
 __global__ void __launch_bounds__(kThreads, 1) ffi_grad_w_kernel(GradWKernelParams p) {
     constexpr int BT = 32 * BPL;
+    const TX* xT = static_cast<const TX*>(p.xT);
     constexpr int LOG2G = G == 32 ? 5 : (G == 16 ? 4 : (G == 8 ? 3 : 2));
     using V = typename Vec<BPL>::type;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -88,7 +91,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_grad_w_kernel(GradWKernelPara
             int i = e / BT;
             int bl = e - i * BT;
             int b = b0 + bl;
-            float v = b < p.B ? p.xT[static_cast<size_t>(i) * p.ldx + b] : 0.f;
+            float v = b < p.B ? widen(xT[static_cast<size_t>(i) * p.ldx + b]) : 0.f;
             x_s[i * BT + (bl & 31) * BPL + (bl >> 5)] = v;
         }
     }
@@ -114,7 +117,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_grad_w_kernel(GradWKernelPara
     };
 
     const V* xs_lane = reinterpret_cast<const V*>(x_s) + lane;
-    const V* xg_lane = reinterpret_cast<const V*>(p.xT + b0) + lane;
+    const TX* xg_base = xT + b0;
     const size_t ldv = static_cast<size_t>(p.ldx / BPL);
 
     // The g tile of the next output tile is fetched into registers while the current tile is
@@ -202,10 +205,10 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_grad_w_kernel(GradWKernelPara
                         v2 = xs_lane[ii.z * 32];
                         v3 = xs_lane[ii.w * 32];
                     } else {
-                        v0 = __ldg(xg_lane + ii.x * ldv);
-                        v1 = __ldg(xg_lane + ii.y * ldv);
-                        v2 = __ldg(xg_lane + ii.z * ldv);
-                        v3 = __ldg(xg_lane + ii.w * ldv);
+                        v0 = load_lane_vec<BPL>(xg_base, static_cast<size_t>(ii.x) * ldv + lane);
+                        v1 = load_lane_vec<BPL>(xg_base, static_cast<size_t>(ii.y) * ldv + lane);
+                        v2 = load_lane_vec<BPL>(xg_base, static_cast<size_t>(ii.z) * ldv + lane);
+                        v3 = load_lane_vec<BPL>(xg_base, static_cast<size_t>(ii.w) * ldv + lane);
                     }
                     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
@@ -251,9 +254,9 @@ int gw_pick_TO(size_t budget, int N, int bpl, bool xsmem, int Kp) {
     return static_cast<int>(to / 16 * 16);
 }
 
-template <int BPL, int G, bool XSMEM>
+template <int BPL, int G, bool XSMEM, typename TX>
 int launch_gw_t(GradWKernelParams p, size_t smem, int nBT, const DeviceInfo& dev, cudaStream_t stream) {
-    auto kern = ffi_grad_w_kernel<BPL, G, XSMEM>;
+    auto kern = ffi_grad_w_kernel<BPL, G, XSMEM, TX>;
     FFI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(smem)));
     int occ = 0;
@@ -270,15 +273,28 @@ int launch_gw_t(GradWKernelParams p, size_t smem, int nBT, const DeviceInfo& dev
     return FFI_OK;
 }
 
-template <int BPL, bool XSMEM>
+template <int BPL, bool XSMEM, typename TX>
 int launch_gw_g(const GradWKernelParams& p, int G, size_t smem, int nBT, const DeviceInfo& dev,
                 cudaStream_t stream) {
     switch (G) {
-        case 4: return launch_gw_t<BPL, 4, XSMEM>(p, smem, nBT, dev, stream);
-        case 8: return launch_gw_t<BPL, 8, XSMEM>(p, smem, nBT, dev, stream);
-        case 16: return launch_gw_t<BPL, 16, XSMEM>(p, smem, nBT, dev, stream);
-        default: return launch_gw_t<BPL, 32, XSMEM>(p, smem, nBT, dev, stream);
+        case 4: return launch_gw_t<BPL, 4, XSMEM, TX>(p, smem, nBT, dev, stream);
+        case 8: return launch_gw_t<BPL, 8, XSMEM, TX>(p, smem, nBT, dev, stream);
+        case 16: return launch_gw_t<BPL, 16, XSMEM, TX>(p, smem, nBT, dev, stream);
+        default: return launch_gw_t<BPL, 32, XSMEM, TX>(p, smem, nBT, dev, stream);
     }
+}
+
+template <typename TX>
+int launch_gw_x(const GradWKernelParams& p, int G, size_t smem, int nBT, int bpl, bool xsmem, const DeviceInfo& dev,
+                cudaStream_t stream) {
+    if (xsmem) {
+        if (bpl == 4) return launch_gw_g<4, true, TX>(p, G, smem, nBT, dev, stream);
+        if (bpl == 2) return launch_gw_g<2, true, TX>(p, G, smem, nBT, dev, stream);
+        return launch_gw_g<1, true, TX>(p, G, smem, nBT, dev, stream);
+    }
+    if (bpl == 4) return launch_gw_g<4, false, TX>(p, G, smem, nBT, dev, stream);
+    if (bpl == 2) return launch_gw_g<2, false, TX>(p, G, smem, nBT, dev, stream);
+    return launch_gw_g<1, false, TX>(p, G, smem, nBT, dev, stream);
 }
 
 int pick_group(int K) {
@@ -358,14 +374,8 @@ int launch_grad_w(const GradWArgs& a, cudaStream_t stream) {
             reinterpret_cast<uintptr_t>(a.xT) % 16 != 0)
             return fail(FFI_ERR_INVALID_ARGUMENT, "wide-N grad_W needs a padded, aligned x copy");
     }
-    if (xsmem) {
-        if (bpl == 4) return launch_gw_g<4, true>(p, G, smem, nBT, dev, stream);
-        if (bpl == 2) return launch_gw_g<2, true>(p, G, smem, nBT, dev, stream);
-        return launch_gw_g<1, true>(p, G, smem, nBT, dev, stream);
-    }
-    if (bpl == 4) return launch_gw_g<4, false>(p, G, smem, nBT, dev, stream);
-    if (bpl == 2) return launch_gw_g<2, false>(p, G, smem, nBT, dev, stream);
-    return launch_gw_g<1, false>(p, G, smem, nBT, dev, stream);
+    if (a.bf16) return launch_gw_x<__nv_bfloat16>(p, G, smem, nBT, bpl, xsmem, dev, stream);
+    return launch_gw_x<float>(p, G, smem, nBT, bpl, xsmem, dev, stream);
 }
 
 }  // namespace ffi

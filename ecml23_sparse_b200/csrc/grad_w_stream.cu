@@ -249,11 +249,11 @@ int launch_grad_w_stream(const GradWArgs& a, cudaStream_t stream, bool* handled)
     if (rc != FFI_OK) return rc;
     size_t smem = 0;
     const int bpl = stream_bpl(a.B, a.N, a.K, a.idx, &smem);
-    if (bpl < 1 || !a.gT) return FFI_OK;
+    if (bpl < 1 || !a.gT || a.bf16) return FFI_OK;  // (this kernel reads fp32 x only)
     int G = 32;
     while (a.K % G != 0) G /= 2;  // K % 4 == 0, so G >= 4
     GradWStreamParams p;
-    p.xT = a.xT;
+    p.xT = static_cast<const float*>(a.xT);
     p.ldx = a.ldx;
     p.idx = a.idx;
     p.gT = a.gT;

@@ -230,8 +230,8 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, float*
 
 // One warp per (input i, batch tile of 32*VEC): walks row i of the canonical index and gathers
 // one row of the transposed gradient gT[L][ldg] per entry.
-template <int VEC>
-__global__ void __launch_bounds__(256) ffi_grad_x_wide_kernel(const float* __restrict__ W,
+template <int VEC, typename TW>
+__global__ void __launch_bounds__(256) ffi_grad_x_wide_kernel(const TW* __restrict__ W,
                                                               const float* __restrict__ gT,
                                                               const int* __restrict__ rowptr,
                                                               const int* __restrict__ perm,
@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(256) ffi_grad_x_wide_kernel(const float* __res
         if (e < t) {
             const int pos = __ldg(perm + e);
             o = pos / K;
-            w = __ldg(W + pos);
+            w = widen(W[pos]);
         }
         const int cnt = min(32, t - base);
         for (int u = 0; u < cnt; ++u) {
@@ -431,6 +431,8 @@ int launch_grad_x(const GradXArgs& a, cudaStream_t stream) {
         return fail(FFI_ERR_INVALID_ARGUMENT, "grad_x needs the transposed upstream gradient");
 
     NarrowConfig c;
+    if (a.w_bf16 && plan->has_chunks)
+        return fail(FFI_ERR_UNSUPPORTED, "the narrow-input grad_x kernel reads fp32 weights");
     // a caller with little scratch (the allocation-free entry point) gets longer segments
     if (narrow_config(plan, a.B, dev, &c, a.workspace_bytes < (static_cast<size_t>(256) << 20) ? a.workspace_bytes
                                                                                                 : (static_cast<size_t>(256) << 20))) {
@@ -441,7 +443,7 @@ int launch_grad_x(const GradXArgs& a, cudaStream_t stream) {
             return fail(FFI_ERR_WORKSPACE, "workspace must be 16-byte aligned");
         if (a.ldg < c.Bpad) return fail(FFI_ERR_INVALID_ARGUMENT, "transposed gradient stride too small");
         GxNarrowParams p;
-        p.W = a.W;
+        p.W = static_cast<const float*>(a.W);
         p.gT = a.gT;
         p.ldg = a.ldg;
         p.cperm = plan->cperm;
@@ -473,15 +475,19 @@ int launch_grad_x(const GradXArgs& a, cudaStream_t stream) {
     const int vec = a.ldg % 128 == 0 ? 4 : (a.ldg % 64 == 0 ? 2 : 1);
     const long long warps = static_cast<long long>(a.N) * (a.ldg / (32 * vec));
     const unsigned blocks = static_cast<unsigned>(ceil_div(warps, 8));
-    if (vec == 4)
-        ffi_grad_x_wide_kernel<4><<<blocks, 256, 0, stream>>>(a.W, a.gT, plan->rowptr, plan->perm, a.gx, a.B, a.N,
-                                                              a.K, a.ldg, a.x_transposed);
-    else if (vec == 2)
-        ffi_grad_x_wide_kernel<2><<<blocks, 256, 0, stream>>>(a.W, a.gT, plan->rowptr, plan->perm, a.gx, a.B, a.N,
-                                                              a.K, a.ldg, a.x_transposed);
-    else
-        ffi_grad_x_wide_kernel<1><<<blocks, 256, 0, stream>>>(a.W, a.gT, plan->rowptr, plan->perm, a.gx, a.B, a.N,
-                                                              a.K, a.ldg, a.x_transposed);
+    auto launch_wide = [&](auto w_typed) {
+        if (vec == 4)
+            ffi_grad_x_wide_kernel<4><<<blocks, 256, 0, stream>>>(w_typed, a.gT, plan->rowptr, plan->perm, a.gx, a.B, a.N,
+                                                                  a.K, a.ldg, a.x_transposed);
+        else if (vec == 2)
+            ffi_grad_x_wide_kernel<2><<<blocks, 256, 0, stream>>>(w_typed, a.gT, plan->rowptr, plan->perm, a.gx, a.B, a.N,
+                                                                  a.K, a.ldg, a.x_transposed);
+        else
+            ffi_grad_x_wide_kernel<1><<<blocks, 256, 0, stream>>>(w_typed, a.gT, plan->rowptr, plan->perm, a.gx, a.B, a.N,
+                                                                  a.K, a.ldg, a.x_transposed);
+    };
+    if (a.w_bf16) launch_wide(static_cast<const __nv_bfloat16*>(a.W));
+    else launch_wide(static_cast<const float*>(a.W));
     FFI_LAUNCH_CHECK("ffi_grad_x_wide_kernel");
     return FFI_OK;
 }
@@ -556,6 +562,7 @@ extern "C" int ffi_grad_x_static(const float* W, const float* gT, int64_t ldg, c
     GradXArgs a;
     a.idx = nullptr;
     a.W = W;
+    a.w_bf16 = false;
     a.g = nullptr;
     a.gT = gT;
     a.ldg = ldg;

@@ -107,8 +107,12 @@ __global__ void bce_finalize_kernel(const int* __restrict__ row_ptr, const int* 
 // the positives (BCE: scale * (sigmoid(z) - 1); squared hinge: -2 * scale * max(0, 1 - z); hinge: -scale
 // where z < 1), recomputing z of the few positive (b,o) pairs.  One block per sample; pos_partials[b] = the sample's sum of
 // loss(z, target 1) - loss(z, target 0) over its positives (fixed order).
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
 __global__ void __launch_bounds__(256) bce_positive_fix_kernel(
-    const float* __restrict__ xT, long long ldx, const int* __restrict__ idx, const float* __restrict__ W,
+    const T* __restrict__ xT, long long ldx, const int* __restrict__ idx, const T* __restrict__ W,
     const float* __restrict__ bias, const int* __restrict__ row_ptr, const int* __restrict__ labels,
     float* __restrict__ gT, long long ldg, double* __restrict__ pos_partials, float scale, long long L, int K,
     long long label_offset, int loss_kind) {
@@ -123,7 +127,7 @@ __global__ void __launch_bounds__(256) bce_positive_fix_kernel(
         float z = 0.f;
         for (int k = lane; k < K; k += 32) {
             const int i = idx[o * K + k];
-            z = fmaf(W[o * K + k], xT[static_cast<size_t>(i) * ldx + b], z);
+            z = fmaf(to_f32(W[o * K + k]), to_f32(xT[static_cast<size_t>(i) * ldx + b]), z);
         }
 #pragma unroll
         for (int off = 16; off >= 1; off /= 2) z += __shfl_xor_sync(0xffffffffu, z, off);
@@ -247,12 +251,19 @@ int launch_widen_bf16(const void* src, float* dst, int64_t n, cudaStream_t strea
     return FFI_OK;
 }
 
-int launch_bce_positive_fix(const float* xT, int64_t ldx, const int* idx, const float* W, const float* bias,
+// xT and W are fp32, or bf16 when `bf16` is set.
+int launch_bce_positive_fix(const void* xT, int64_t ldx, const int* idx, const void* W, const float* bias,
                             const int* row_ptr, const int* labels, float* gT, int64_t ldg, float* loss,
                             const double* partials, int nPartials, double* pos_partials, float scale, int B,
-                            int64_t L, int K, int64_t label_offset, int loss_kind, cudaStream_t stream) {
-    bce_positive_fix_kernel<<<static_cast<unsigned>(B), 256, 0, stream>>>(
-        xT, ldx, idx, W, bias, row_ptr, labels, gT, ldg, pos_partials, scale, L, K, label_offset, loss_kind);
+                            int64_t L, int K, int64_t label_offset, int loss_kind, bool bf16, cudaStream_t stream) {
+    if (bf16)
+        bce_positive_fix_kernel<__nv_bfloat16><<<static_cast<unsigned>(B), 256, 0, stream>>>(
+            static_cast<const __nv_bfloat16*>(xT), ldx, idx, static_cast<const __nv_bfloat16*>(W), bias, row_ptr, labels,
+            gT, ldg, pos_partials, scale, L, K, label_offset, loss_kind);
+    else
+        bce_positive_fix_kernel<float><<<static_cast<unsigned>(B), 256, 0, stream>>>(
+            static_cast<const float*>(xT), ldx, idx, static_cast<const float*>(W), bias, row_ptr, labels, gT, ldg,
+            pos_partials, scale, L, K, label_offset, loss_kind);
     if (loss) bce_loss_finalize_kernel<<<1, 256, 0, stream>>>(partials, nPartials, pos_partials, B, scale, loss);
     FFI_LAUNCH_CHECK("bce_positive_fix_kernel");
     return FFI_OK;

@@ -259,8 +259,9 @@ def forward_bce(features, lookup, weights, bias, row_ptr, labels, transposed: bo
 
     The logits are never materialised.  Raises FFIError (FFI_ERR_UNSUPPORTED) for shapes the fused
     kernel does not cover; use `_forward` + `sparse_bce_with_logits` there."""
-    features = _check_cuda("features", features, (torch.float32,))
-    weights = _check_cuda("weights", weights, (torch.float32,))
+    features = _check_cuda("features", features, _STORAGE_DTYPES)
+    weights = _check_cuda("weights", weights, _STORAGE_DTYPES)
+    dtype = _storage_dtype(features, weights)
     lookup = _as_index(lookup)
     B, N, L, K = _shapes(features, lookup, weights, transposed)
     dev = features.device
@@ -273,7 +274,7 @@ def forward_bce(features, lookup, weights, bias, row_ptr, labels, transposed: bo
     gT = torch.empty((L, ldg), dtype=torch.float32, device=dev)
     loss_out = torch.empty((), dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
-        ws_bytes = lib.ffi_forward_bce_workspace_bytes(B, N, L, K, int(transposed), _lib.FFI_F32)
+        ws_bytes = lib.ffi_forward_bce_workspace_bytes(B, N, L, K, int(transposed), dtype)
         ws = _workspace(dev, ws_bytes + 256)
         off = (-ws.data_ptr()) % 256
         kind = {"bce": _lib.FFI_LOSS_BCE, "squared_hinge": _lib.FFI_LOSS_SQUARED_HINGE, "hinge": _lib.FFI_LOSS_HINGE}[loss]
@@ -281,7 +282,7 @@ def forward_bce(features, lookup, weights, bias, row_ptr, labels, transposed: bo
                                         bias.data_ptr() if bias is not None else None, row_ptr.data_ptr(),
                                         labels.data_ptr() if labels.numel() else row_ptr.data_ptr(), gT.data_ptr(),
                                         loss_out.data_ptr(), B, N, L, K, total_labels or L, label_offset,
-                                        int(transposed), _lib.FFI_F32, ws.data_ptr() + off, ws.numel() - off,
+                                        int(transposed), dtype, ws.data_ptr() + off, ws.numel() - off,
                                         _stream_ptr(dev)))
     return loss_out, gT
 

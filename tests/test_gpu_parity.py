@@ -599,7 +599,9 @@ def test_fused_forward_loss_on_tiled_kernel_shapes(cuda_device, shape, loss_name
 
 
 @pytest.mark.parametrize("shape,transposed", [((64, 512, 3_001, 32), True), ((37, 254, 513, 16), False),
-                                              ((130, 100, 600, 73), False)], ids=["wiki-like", "small", "odd"])
+                                              ((130, 100, 600, 73), False), ((128, 768, 20_011, 32), True),
+                                              ((100, 300, 2_001, 64), False), ((128, 32_768, 1_001, 32), True)],
+                         ids=["wiki-like", "small", "odd", "headline-like", "K64-staged-x", "wide"])
 def test_bf16_storage_of_x_and_w(cuda_device, shape, transposed):
     """x and W stored as bf16, fp32 accumulation (benchmark configurations 2-4; the reference is fp32
     only, tfsparse/cc/kernels/register.cpp:79-109).  Inputs are rounded to bf16 once; the CUDA result
@@ -627,3 +629,12 @@ def test_bf16_storage_of_x_and_w(cuda_device, shape, transposed):
         assert np.abs(got - ref).max() <= 2e-2 * scale, f"bf16 {what} further than 2e-2 from the fp32-input result"
     with pytest.raises(TypeError):
         ops._forward(xin, to_cuda(idx, dev), to_cuda(W, dev), None, transposed)  # mixed storage types
+    # the fused loss on bf16 storage: same logits, so the same gradient as the oracle's on the rounded inputs
+    bias = synth.normal(17, 40, (L,), std=0.5).numpy()
+    row_ptr, labels = synth.multi_hot_targets(17, 41, B, L)
+    loss, gT = ops.forward_bce(xin, to_cuda(idx, dev), Wb.to(dev), to_cuda(bias, dev), row_ptr, labels, transposed)
+    z = oracle.forward_f64(xr, idx, Wr, bias=bias).astype(np.float32)
+    loss_ref, g_ref = oracle.bce_f64(z, row_ptr.numpy(), labels.numpy())
+    assert abs(float(loss) - loss_ref) <= 2e-5 * abs(loss_ref) + 1e-7
+    assert_close(gT[:, :B].t().cpu().numpy(), g_ref, 5e-5, 2e-7 / (B * L), "fused BCE gradient on bf16 storage")
+    assert not gT[:, B:].any()
