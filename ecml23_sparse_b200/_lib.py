@@ -29,7 +29,7 @@ FFI_LOSS_HINGE = 2
 
 # Every symbol include/ffi_b200.h declares.
 EXPORTED_SYMBOLS = (
-    "ffi_last_error", "ffi_version",
+    "ffi_last_error", "ffi_version", "ffi_set_debug_bounds",
     "ffi_forward_workspace_bytes", "ffi_forward",
     "ffi_plan_create", "ffi_plan_rebuild", "ffi_plan_destroy", "ffi_plan_info", "ffi_plan_export", "ffi_plan_export_chunked",
     "ffi_backward_workspace_bytes", "ffi_backward",
@@ -60,6 +60,8 @@ def _declare(lib):
     lib.ffi_last_error.restype = ctypes.c_char_p
     lib.ffi_last_error.argtypes = []
     lib.ffi_version.restype = i32
+    lib.ffi_set_debug_bounds.restype = i32
+    lib.ffi_set_debug_bounds.argtypes = [i32]
     lib.ffi_forward_workspace_bytes.restype = sz
     lib.ffi_forward_workspace_bytes.argtypes = [i64, i64, i64, i64, i32, i32]
     lib.ffi_forward.restype = i32

@@ -220,10 +220,15 @@ extern "C" size_t ffi_forward_workspace_bytes(int64_t B, int64_t N, int64_t L, i
 extern "C" int ffi_forward(const void* x, const int32_t* idx, const void* W, const float* bias, float* y,
                            int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed, int dtype,
                            void* workspace, size_t workspace_bytes, void* stream_v) {
+    FFI_TRACE("ffi_forward");
     if (!x || !idx || !W || !y) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_forward");
     int rc = check_shape(B, N, L, K);
     if (rc != FFI_OK) return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (debug_bounds_enabled()) {
+        rc = check_index_range(idx, L * K, N, stream);
+        if (rc != FFI_OK) return rc;
+    }
     if (dtype == FFI_BF16) {
         // native bf16 kernel (x tile and W rows stay bf16 in shared memory) where the shape allows it
         if (forward_bf16_warps(B, N, K, false) >= 4) {
@@ -294,6 +299,7 @@ extern "C" int64_t ffi_transposed_gradient_stride(int64_t B) { return B > 0 ? tr
 
 extern "C" int ffi_transpose_gradient(const float* g, float* gT, float* grad_bias, int64_t B, int64_t L,
                                       void* stream_v) {
+    FFI_TRACE("ffi_transpose_gradient");
     if (!g || !gT) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_transpose_gradient");
     if (B <= 0 || L <= 0 || B >= (1LL << 31) - 1 || L >= (1LL << 31) - 1)
         return fail(FFI_ERR_INVALID_ARGUMENT, "B and L must be positive and fit 32 bits");
@@ -330,6 +336,10 @@ static int backward_impl(const void* x, const int32_t* idx, const void* W, const
     int rc = check_shape(B, N, L, K);
     if (rc != FFI_OK) return rc;
     if (dtype != FFI_F32 && dtype != FFI_BF16) return fail(FFI_ERR_UNSUPPORTED, "ffi_backward: dtype %d not supported", dtype);
+    if (debug_bounds_enabled()) {
+        rc = check_index_range(idx, L * K, N, static_cast<cudaStream_t>(stream_v));
+        if (rc != FFI_OK) return rc;
+    }
     // bf16 storage: the group kernel (one pass, batch <= 128) and the kernels for wide inputs read bf16 x and W
     // themselves; for the other shapes both are widened (exactly) into the workspace and the fp32 kernels run.
     bool bf16 = false;
@@ -486,6 +496,7 @@ extern "C" int ffi_backward(const void* x, const int32_t* idx, const void* W, co
                             const ffi_plan* plan, float* grad_x, float* grad_w, float* grad_bias, int64_t B,
                             int64_t N, int64_t L, int64_t K, int x_transposed, int dtype, void* workspace,
                             size_t workspace_bytes, void* stream_v) {
+    FFI_TRACE("ffi_backward");
     if (!g) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_backward");
     return backward_impl(x, idx, W, g, nullptr, 0, plan, grad_x, grad_w, grad_bias, B, N, L, K, x_transposed, dtype,
                          workspace, workspace_bytes, stream_v);
@@ -496,6 +507,7 @@ extern "C" int ffi_backward_from_transposed(const void* x, const int32_t* idx, c
                                             float* grad_bias, int64_t B, int64_t N, int64_t L, int64_t K,
                                             int x_transposed, int dtype, void* workspace, size_t workspace_bytes,
                                             void* stream_v) {
+    FFI_TRACE("ffi_backward_from_transposed");
     if (!gT) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_backward_from_transposed");
     return backward_impl(x, idx, W, nullptr, gT, ldg, plan, grad_x, grad_w, grad_bias, B, N, L, K, x_transposed, dtype,
                          workspace, workspace_bytes, stream_v);
@@ -526,6 +538,7 @@ extern "C" int ffi_forward_loss(int loss_kind, const void* x, const int32_t* idx
                                 const int32_t* row_ptr, const int32_t* labels, float* gT, float* loss, int64_t B,
                                 int64_t N, int64_t L, int64_t K, int64_t L_total, int64_t label_offset,
                                 int x_transposed, int dtype, void* workspace, size_t workspace_bytes, void* stream_v) {
+    FFI_TRACE("ffi_forward_loss");
     if (!x || !idx || !W || !row_ptr || !labels || !gT)
         return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_forward_loss");
     if (loss_kind != FFI_LOSS_BCE && loss_kind != FFI_LOSS_SQUARED_HINGE && loss_kind != FFI_LOSS_HINGE)
@@ -537,6 +550,10 @@ extern "C" int ffi_forward_loss(int loss_kind, const void* x, const int32_t* idx
     if (L_total < L) return fail(FFI_ERR_INVALID_ARGUMENT, "L_total must be >= L");
     if (reinterpret_cast<uintptr_t>(gT) % 16 != 0) return fail(FFI_ERR_INVALID_ARGUMENT, "gT must be 16-byte aligned");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (debug_bounds_enabled()) {
+        rc = check_index_range(idx, L * K, N, stream);
+        if (rc != FFI_OK) return rc;
+    }
     if (!workspace || reinterpret_cast<uintptr_t>(workspace) % kAlign != 0 ||
         workspace_bytes < ffi_forward_bce_workspace_bytes(B, N, L, K, x_transposed, dtype))
         return fail(FFI_ERR_WORKSPACE, "ffi_forward_loss needs %zu bytes of %zu-byte aligned workspace",
@@ -640,6 +657,7 @@ extern "C" int ffi_forward_topk(const void* x, const int32_t* idx, const void* W
                                 int32_t* top_idx, int k, int64_t B, int64_t N, int64_t L, int64_t K,
                                 int64_t label_offset, int x_transposed, int dtype, void* workspace,
                                 size_t workspace_bytes, void* stream_v) {
+    FFI_TRACE("ffi_forward_topk");
     if (!x || !idx || !W || !top_val || !top_idx)
         return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_forward_topk");
     int rc = check_shape(B, N, L, K);

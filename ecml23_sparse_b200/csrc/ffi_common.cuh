@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <cuda_pipeline.h>
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <cstdarg>
 #include <cstdint>
@@ -32,6 +33,21 @@ int fail(int status, const char* fmt, ...);
             return ::ffi::fail(FFI_ERR_CUDA, "launch of %s failed: %s", name,              \
                                cudaGetErrorString(_e));                                    \
     } while (0)
+
+// ---- tracing: an NVTX range around every entry point (a no-op unless a profiler is attached) --------
+struct TraceRange {
+    explicit TraceRange(const char* name) { nvtxRangePushA(name); }
+    ~TraceRange() { nvtxRangePop(); }
+    TraceRange(const TraceRange&) = delete;
+    TraceRange& operator=(const TraceRange&) = delete;
+};
+#define FFI_TRACE(name) ::ffi::TraceRange ffi_trace_range_(name)
+
+// ---- debug bounds: with ffi_set_debug_bounds(1) (or FFI_DEBUG_BOUNDS=1 in the environment) every entry
+// point that reads an index table first checks that all its values lie in [0, N) and returns
+// FFI_ERR_INDEX_RANGE otherwise (one extra pass over idx and a stream synchronisation per call) ------------
+bool debug_bounds_enabled();
+int check_index_range(const int32_t* idx, int64_t n, int64_t N, cudaStream_t stream);
 
 // ---- device properties (cached per device) ---------------------------------------
 struct DeviceInfo {

@@ -536,6 +536,7 @@ extern "C" size_t ffi_grad_x_static_max_scratch_bytes(void) { return ffi::kStati
 
 extern "C" int ffi_grad_x_static(const float* W, const float* gT, int64_t ldg, const ffi_plan* plan, float* grad_x,
                                  int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed, void* stream_v) {
+    FFI_TRACE("ffi_grad_x_static");
     using namespace ffi;
     if (!W || !gT || !plan || !grad_x) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL argument to ffi_grad_x_static");
     if (B <= 0 || N <= 0 || L <= 0 || K <= 0 || B >= (1LL << 31))

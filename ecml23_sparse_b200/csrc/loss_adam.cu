@@ -229,6 +229,33 @@ __global__ void __launch_bounds__(256) adam_kernel_f32x4(float4* __restrict__ w,
     }
 }
 
+// bf16 weights, four at a time: 8-byte accesses to w, 16-byte accesses to m, v and the gradient
+__global__ void __launch_bounds__(256) adam_kernel_bf16x4(uint2* __restrict__ w, float4* __restrict__ m,
+                                                          float4* __restrict__ v, const float4* __restrict__ grad,
+                                                          long long n4, float alpha, float omb1, float omb2, float eps) {
+    const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long e = tid; e < n4; e += stride) {
+        const float4 gj = grad[e];
+        float4 mj = m[e], vj = v[e];
+        const uint2 wr = w[e];
+        float4 wj = make_float4(bf16_lo(wr.x), bf16_hi(wr.x), bf16_lo(wr.y), bf16_hi(wr.y));
+#define FFI_ADAM_LANE(c)                                     \
+    mj.c += (gj.c - mj.c) * omb1;                            \
+    vj.c += (gj.c * gj.c - vj.c) * omb2;                     \
+    wj.c -= alpha * mj.c / (sqrtf(vj.c) + eps);
+        FFI_ADAM_LANE(x) FFI_ADAM_LANE(y) FFI_ADAM_LANE(z) FFI_ADAM_LANE(w)
+#undef FFI_ADAM_LANE
+        m[e] = mj;
+        v[e] = vj;
+        const unsigned lo = __bfloat16_as_ushort(__float2bfloat16_rn(wj.x)) |
+                            (static_cast<unsigned>(__bfloat16_as_ushort(__float2bfloat16_rn(wj.y))) << 16);
+        const unsigned hi = __bfloat16_as_ushort(__float2bfloat16_rn(wj.z)) |
+                            (static_cast<unsigned>(__bfloat16_as_ushort(__float2bfloat16_rn(wj.w))) << 16);
+        w[e] = make_uint2(lo, hi);
+    }
+}
+
 }  // namespace
 }  // namespace ffi
 
@@ -283,6 +310,7 @@ extern "C" size_t ffi_bce_workspace_bytes(int64_t, int64_t) { return (1 + kBceBl
 extern "C" int ffi_bce_grad(const float* z, const int32_t* row_ptr, const int32_t* labels, float* g,
                             float* loss, int64_t B, int64_t L, int64_t L_total, int64_t label_offset,
                             void* workspace, size_t workspace_bytes, void* stream_v) {
+    FFI_TRACE("ffi_bce_grad");
     if (!z || !row_ptr || !labels || !g) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL argument to ffi_bce_grad");
     if (B <= 0 || L <= 0 || L_total < L || B >= (1LL << 31))
         return fail(FFI_ERR_INVALID_ARGUMENT, "bad shape B=%lld L=%lld L_total=%lld", (long long)B,
@@ -306,6 +334,7 @@ extern "C" int ffi_bce_grad(const float* z, const int32_t* row_ptr, const int32_
 
 extern "C" int ffi_adam_step(void* w, float* m, float* v, const float* grad, int64_t n, float lr, float beta1,
                              float beta2, float eps, int64_t step, int dtype, void* stream_v) {
+    FFI_TRACE("ffi_adam_step");
     if (!w || !m || !v || !grad) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL argument to ffi_adam_step");
     if (n <= 0 || step < 1) return fail(FFI_ERR_INVALID_ARGUMENT, "n must be positive and step >= 1");
     if (dtype != FFI_F32 && dtype != FFI_BF16) return fail(FFI_ERR_UNSUPPORTED, "unknown dtype %d", dtype);
@@ -319,7 +348,20 @@ extern "C" int ffi_adam_step(void* w, float* m, float* v, const float* grad, int
     if (rc != FFI_OK) return rc;
     const unsigned blocks = static_cast<unsigned>(dev.sm_count * 8);
     if (dtype == FFI_BF16) {
-        adam_kernel<true><<<blocks, 256, 0, stream>>>(w, m, v, grad, n, alpha, omb1, omb2, eps);
+        const bool aligned = reinterpret_cast<uintptr_t>(w) % 8 == 0 &&
+                             ((reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+                               reinterpret_cast<uintptr_t>(grad)) % 16) == 0;
+        const long long n4 = aligned ? n / 4 : 0;
+        if (n4 > 0)
+            adam_kernel_bf16x4<<<blocks, 256, 0, stream>>>(static_cast<uint2*>(w), reinterpret_cast<float4*>(m),
+                                                           reinterpret_cast<float4*>(v),
+                                                           reinterpret_cast<const float4*>(grad), n4, alpha, omb1, omb2,
+                                                           eps);
+        const long long rest = n - n4 * 4;
+        if (rest > 0)
+            adam_kernel<true><<<aligned ? 1 : blocks, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(w) + n4 * 4,
+                                                                       m + n4 * 4, v + n4 * 4, grad + n4 * 4, rest, alpha,
+                                                                       omb1, omb2, eps);
     } else {
         const bool aligned = ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(m) |
                                reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(grad)) % 16) == 0;

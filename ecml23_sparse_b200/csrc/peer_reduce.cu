@@ -120,6 +120,7 @@ using namespace ffi;
 
 extern "C" int ffi_peer_sum(const void* const* peer_bufs, void* const* peer_flags, int rank, int world, int64_t n,
                             uint32_t step, float* out, void* stream_v) {
+    FFI_TRACE("ffi_peer_sum");
     if (!peer_bufs || !peer_flags || !out) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL argument passed to ffi_peer_sum");
     if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
         return fail(FFI_ERR_INVALID_ARGUMENT, "ffi_peer_sum supports 1..%d ranks", kMaxPeers);

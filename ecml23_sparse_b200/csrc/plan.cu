@@ -13,6 +13,9 @@
 // cperm[c*T*K ...], with cptr[c][i] the offset of input i's run inside the chunk.
 // Concatenating, for each input i, its runs over the chunks in chunk order gives back
 // exactly row i of the canonical form (chunks are ascending ranges of p).
+#include <atomic>
+#include <cstdlib>
+
 #include "ffi_common.cuh"
 
 namespace ffi {
@@ -457,8 +460,44 @@ int plan_build(ffi_plan* plan, const int32_t* idx, unsigned char* scratch, cudaS
 }  // namespace
 }  // namespace ffi
 
+namespace ffi {
+namespace {
+__device__ int g_bounds_bad = 0;
+std::atomic<int> g_debug_bounds{-1};  // -1: not decided yet (environment), 0: off, 1: on
+}  // namespace
+
+bool debug_bounds_enabled() {
+    int v = g_debug_bounds.load();
+    if (v < 0) {
+        const char* e = std::getenv("FFI_DEBUG_BOUNDS");
+        v = (e && e[0] != '\0' && e[0] != '0') ? 1 : 0;
+        g_debug_bounds.store(v);
+    }
+    return v == 1;
+}
+
+int check_index_range(const int32_t* idx, int64_t n, int64_t N, cudaStream_t stream) {
+    int zero = 0, h_bad = 0;
+    FFI_CUDA_CHECK(cudaMemcpyToSymbolAsync(g_bounds_bad, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream));
+    int* bad = nullptr;
+    FFI_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&bad), g_bounds_bad));
+    validate_idx_kernel<<<1024, 256, 0, stream>>>(idx, n, static_cast<int>(N), bad);
+    FFI_LAUNCH_CHECK("validate_idx_kernel");
+    FFI_CUDA_CHECK(cudaMemcpyAsync(&h_bad, bad, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    FFI_CUDA_CHECK(cudaStreamSynchronize(stream));
+    if (h_bad) return fail(FFI_ERR_INDEX_RANGE, "debug bounds: idx holds a value outside [0, %lld)", (long long)N);
+    return FFI_OK;
+}
+}  // namespace ffi
+
+extern "C" int ffi_set_debug_bounds(int on) {
+    ffi::g_debug_bounds.store(on ? 1 : 0);
+    return FFI_OK;
+}
+
 extern "C" int ffi_plan_create(const int32_t* idx, int64_t L, int64_t K, int64_t N, void* stream_v,
                                ffi_plan** out_plan) {
+    FFI_TRACE("ffi_plan_create");
     if (!out_plan) return fail(FFI_ERR_INVALID_ARGUMENT, "out_plan is NULL");
     *out_plan = nullptr;
     if (!idx) return fail(FFI_ERR_INVALID_ARGUMENT, "idx is NULL");
@@ -508,6 +547,7 @@ extern "C" int ffi_plan_create(const int32_t* idx, int64_t L, int64_t K, int64_t
 }
 
 extern "C" int ffi_plan_rebuild(ffi_plan* plan, const int32_t* idx, void* stream_v) {
+    FFI_TRACE("ffi_plan_rebuild");
     if (!plan || !idx) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL argument to ffi_plan_rebuild");
     int rc = check_plan_device(plan);
     if (rc != FFI_OK) return rc;

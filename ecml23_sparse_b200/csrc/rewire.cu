@@ -114,6 +114,7 @@ extern "C" size_t ffi_rewire_workspace_bytes(void) { return sizeof(SelectState);
 extern "C" int ffi_rewire(const float* w, int32_t* idx, float* m, float* v, int64_t n, int64_t n_in,
                           int64_t num_selected, uint64_t seed, float* threshold_out, int32_t* count_out,
                           void* workspace, size_t workspace_bytes, void* stream_v) {
+    FFI_TRACE("ffi_rewire");
     if (!w || !idx) return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_rewire");
     if ((m == nullptr) != (v == nullptr)) return fail(FFI_ERR_INVALID_ARGUMENT, "m and v must both be given or both be NULL");
     if (n <= 0 || n >= (1LL << 31) || n_in <= 0 || n_in >= (1LL << 31))

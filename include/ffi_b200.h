@@ -52,6 +52,16 @@ const char* ffi_last_error(void);
 /* Library ABI version (major*100 + minor). */
 int ffi_version(void);
 
+/*
+ * Debug bounds checking (off by default; also switched on by FFI_DEBUG_BOUNDS=1 in the environment).  When on,
+ * ffi_forward, ffi_forward_loss and the backward entry points first check that every value of idx lies in
+ * [0, N) and return FFI_ERR_INDEX_RANGE instead of launching their kernels: the counterpart of the device-side
+ * index asserts of the reference's audit build (tfsparse/cc/kernels/kernel_data.cu.h:26-43,211), as a status
+ * code instead of a trap.  Costs one pass over idx and a stream synchronisation per call.
+ * Every entry point also opens an NVTX range of its own name, visible to a profiler that is attached.
+ */
+int ffi_set_debug_bounds(int on);
+
 /* ---------------------------------------------------------------- forward ---- */
 
 /* Bytes of scratch ffi_forward needs for this shape (0 when none is needed). */

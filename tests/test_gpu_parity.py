@@ -182,6 +182,33 @@ def test_plan_rejects_out_of_range_index_and_stale_shape(cuda_device):
     assert e.value.status == 5
 
 
+def test_debug_bounds_mode_rejects_bad_indices_before_any_kernel_runs(cuda_device):
+    """With debug bounds on, an index outside [0, N) makes forward / fused loss / backward return
+    FFI_ERR_INDEX_RANGE without launching their kernels (the status-code counterpart of the reference's
+    audit-mode index asserts, tfsparse/cc/kernels/kernel_data.cu.h:26-43,211)."""
+    dev = cuda_device
+    from ecml23_sparse_b200 import ops
+    lib = _lib.load()
+    x, idx, W, g = reference_style_inputs((12, 8, 32, 16))
+    good = to_cuda(idx, dev)
+    bad = good.clone()
+    bad[5, 3] = 8            # N = 8: one past the end
+    row_ptr, labels = synth.multi_hot_targets(1, 2, 12, 32)
+    plan = ffi.FFIPlan(good, 8)
+    _lib.check(lib.ffi_set_debug_bounds(1))
+    try:
+        y = ops._forward(to_cuda(x, dev), good, to_cuda(W, dev), None, False)   # a valid table passes
+        assert_close(y.cpu().numpy(), oracle.forward_f64(x, idx, W), RTOL, ATOL, "y with debug bounds on")
+        for call in (lambda: ops._forward(to_cuda(x, dev), bad, to_cuda(W, dev), None, False),
+                     lambda: ops.forward_bce(to_cuda(x, dev), bad, to_cuda(W, dev), None, row_ptr, labels, False),
+                     lambda: ops._backward(to_cuda(x, dev), bad, to_cuda(W, dev), to_cuda(g, dev), False, plan=plan)):
+            with pytest.raises(_lib.FFIError) as e:
+                call()
+            assert e.value.status == 6
+    finally:
+        _lib.check(lib.ffi_set_debug_bounds(0))
+
+
 def test_plan_cache_follows_tensor_version(cuda_device):
     dev = cuda_device
     x, idx, W, g = reference_style_inputs((12, 8, 32, 16))
@@ -241,6 +268,30 @@ def test_fused_adam_matches_oracle(cuda_device, n):
     assert_close(w.cpu().numpy(), wr, 1e-5, 1e-6, "adam w")
     assert_close(opt.m[0].cpu().numpy(), mr, 1e-5, 1e-7, "adam m")
     assert_close(opt.v[0].cpu().numpy(), vr, 1e-5, 1e-9, "adam v")
+
+
+@pytest.mark.parametrize("n", [5, 4096, 100_003])
+def test_fused_adam_on_bf16_weights(cuda_device, n):
+    """bf16 storage of W (benchmark configurations 2-4): m, v and the update are fp32, the new weight is rounded
+    to bf16 once.  Against the fp64 oracle on the same bf16 starting point: m and v to fp32 accuracy, w within
+    one bf16 rounding step (2^-8 relative) of the oracle's unrounded value."""
+    dev = cuda_device
+    w0 = synth.normal(1, 0, (n,)).to(torch.bfloat16)
+    w = w0.clone().to(dev)
+    opt = ffi.FusedAdam([w], lr=1e-3, beta_1=0.9, beta_2=0.999, epsilon=1e-7)
+    lr, b1, b2, eps = (float(np.float32(v)) for v in (1e-3, 0.9, 0.999, 1e-7))
+    wr, mr, vr = w0.double().numpy(), np.zeros(n), np.zeros(n)
+    for step in range(1, 4):
+        grad = synth.normal(2, step, (n,)).numpy()
+        w_before = w.double().cpu().numpy()
+        opt.step([to_cuda(grad, dev)])
+        # the oracle restarts from the device's rounded weights, so that rounding does not accumulate between steps
+        wr, mr, vr = oracle.adam_f64(w_before, mr, vr, grad.astype(np.float64), lr, b1, b2, eps, step)
+        got = w.double().cpu().numpy()
+        assert np.all(np.abs(got - wr) <= np.abs(wr) * 2.0 ** -8 + 1e-30), "bf16 weight further than one rounding step"
+    assert w.dtype == torch.bfloat16
+    assert_close(opt.m[0].cpu().numpy(), mr, 1e-5, 1e-7, "adam m (bf16 W)")
+    assert_close(opt.v[0].cpu().numpy(), vr, 1e-5, 1e-9, "adam v (bf16 W)")
 
 
 def test_layer_module_matches_oracle(cuda_device):
