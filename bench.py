@@ -55,6 +55,8 @@ def parse_args():
     ap.add_argument("--units", type=int, default=HEADLINE["L"])
     ap.add_argument("--n-in", type=int, default=HEADLINE["N"])
     ap.add_argument("--fan-in", type=int, default=HEADLINE["K"])
+    ap.add_argument("--storage", choices=["f32", "bf16"], default="f32",
+                    help="storage type of x and W (accumulation, y, g and all gradients are fp32 either way)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the extra shapes measured after the headline legs")
@@ -74,12 +76,12 @@ def measured_peaks():
         return FALLBACK_HBM_GBS, "fallback", 1965.0
 
 
-def algorithmic_bytes(B, N, L, K):
-    """Compulsory HBM bytes per pass (fp32 x and W, int32 idx, fp32 y / g / gradients)."""
+def algorithmic_bytes(B, N, L, K, e=4):
+    """Compulsory HBM bytes per pass (x and W of e bytes per value, int32 idx, fp32 y / g / gradients)."""
     return {
-        "forward": L * K * 8 + 4 * L + B * N * 4 + 4 * B * L,
-        "grad_w": 4 * B * L + 4 * L * K + B * N * 4 + 4 * L * K + 4 * L,
-        "grad_x": 4 * B * L + L * K * 8 + 4 * B * N,
+        "forward": L * K * (e + 4) + 4 * L + B * N * e + 4 * B * L,
+        "grad_w": 4 * B * L + 4 * L * K + B * N * e + 4 * L * K + 4 * L,
+        "grad_x": 4 * B * L + L * K * (e + 4) + 4 * B * N,
     }
 
 
@@ -225,9 +227,10 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(B, N, L, K, gpus):
+def workload_config(B, N, L, K, gpus, storage="f32"):
+    kind = "fp32" if storage == "f32" else "bf16 storage of x and W, fp32 accumulation"
     return {
-        "workload": f"single FFI layer fwd+bwd, B={B}, N={N}, L={L}, K={K}, fp32 (op FanInSparseMatmulTp + grad)",
+        "workload": f"single FFI layer fwd+bwd, B={B}, N={N}, L={L}, K={K}, {kind} (op FanInSparseMatmulTp + grad)",
         "B": B, "N": N, "L": L, "K": K,
         "parallelism": f"label-sharded x{gpus}" if gpus > 1 else "single GPU",
         "l2": "256 MiB buffer rewritten between timed steps (L2 flush); per-step CUDA events",
@@ -381,8 +384,12 @@ def run_ours(args):
 
     # ---- inputs resident in HBM -----------------------------------------------------------
     xT = synth.normal(SEED, 0, (N, B), device=dev)
-    idx = synth.indices_without_replacement(SEED, 1, Ls, K, N, device=dev, row_offset=lo)
+    idx = synth.indices_without_replacement(SEED, 1, Ls, K, N, device=dev, row_offset=lo,
+                                            rows_per_block=max(64, min(32768, (1 << 28) // N)))
     W = synth.normal(SEED, 2, (Ls, K), std=(1.0 / K) ** 0.5, device=dev, start=lo * K)
+    store_dtype = torch.bfloat16 if args.storage == "bf16" else torch.float32
+    esize = 2 if args.storage == "bf16" else 4
+    xT, W = xT.to(store_dtype), W.to(store_dtype)
     bias = torch.zeros(Ls, device=dev)
     g = synth.normal(SEED, 3 + 16 * rank, (B, Ls), device=dev)  # upstream gradient of this shard
     plan = ffi.FFIPlan(idx, N)
@@ -549,10 +556,10 @@ def run_ours(args):
     # ---- end to end from host buffers -----------------------------------------------------
     e2e = None
     if not args.no_e2e:
-        x_host = synth.normal(SEED, 0, (N, B)).t().contiguous().pin_memory()          # [B,N] on the host
+        x_host = synth.normal(SEED, 0, (N, B)).t().contiguous().to(store_dtype).pin_memory()  # [B,N] on the host
         rp_host, lab_host = synth.multi_hot_targets(SEED, 5, B, L)
         rp_host, lab_host = rp_host.pin_memory(), lab_host.pin_memory()
-        x_dev = torch.empty((B, N), device=dev)
+        x_dev = torch.empty((B, N), dtype=store_dtype, device=dev)
         rp_dev = torch.empty_like(rp_host, device=dev)
         lab_dev = torch.empty_like(lab_host, device=dev)
         gx_host = torch.empty((B, N)).pin_memory()
@@ -596,7 +603,7 @@ def run_ours(args):
         (e2e_ms, _, _), e2e_reps = median_loop(step_e2e)
         e2e = {
             "value": B / (e2e_ms / args.steps * 1e-3), "unit": "samples/s",
-            "h2d_bytes_per_step": int(x_host.numel() * 4 + rp_host.numel() * 4 + lab_host.numel() * 4),
+            "h2d_bytes_per_step": int(x_host.numel() * esize + rp_host.numel() * 4 + lab_host.numel() * 4),
             "d2h_bytes_per_step": int(gx_host.numel() * 4 + 4),
             "ms_per_step": e2e_ms / args.steps, "ms_per_step_reps": e2e_reps,
             "path": "pinned host x[B,N] + CSR targets -> FanInSparseMatmul(+bias) with fused sigmoid-BCE gradient -> "
@@ -631,7 +638,7 @@ def run_ours(args):
     clocks = sampler.summary(t0, t1)
 
     hbm_gbs, peak_kind, sm_max_mhz = measured_peaks()
-    alg = algorithmic_bytes(B, N, Ls, K)
+    alg = algorithmic_bytes(B, N, Ls, K, esize)
     sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
     fma_peak = sm_count * FMA_PER_CLK_PER_SM * sm_max_mhz * 1e6
     fma_pass = B * Ls * K
@@ -639,10 +646,11 @@ def run_ours(args):
     work = {
         "forward": (alg["forward"], fma_pass),
         "transpose_g": (8 * B * Ls + 4 * Ls, 0),
-        "backward_fused": (4 * B * Ls + 8 * Ls * K + 4 * Ls * K + 8 * B * N, 2 * fma_pass),
+        "backward_fused": (4 * B * Ls + (4 + esize) * Ls * K + 4 * Ls * K + (4 + esize) * B * N, 2 * fma_pass),
     }
     narrow = N <= 2048  # the plan holds the chunked index the one-pass backward walks; x tiles fit shared memory
-    names = {"forward": "ffi_fwd_pair_kernel" if narrow else "ffi_fwd_kernel",
+    names = {"forward": ("ffi_fwd_bf16_kernel" if args.storage == "bf16" and B <= 128 and K % 8 == 0 else
+                         "ffi_fwd_pair_kernel") if narrow else "ffi_fwd_kernel",
              "transpose_g": "transpose_g_kernel",
              "backward_fused": ("ffi_bwd_pairs_kernel" if B > 64 else "ffi_bwd_fused_kernel") if narrow
              else "ffi_grad_w_kernel + ffi_grad_x_wide_kernel"}
@@ -673,7 +681,8 @@ def run_ours(args):
         "kernel": dk["kernel"], "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
         "frac": achieved / peak, "achieved_gbs": dk["achieved_gbs"], "frac_of_hbm_peak": dk["achieved_gbs"] / hbm_gbs,
         "hbm_peak_gbs": hbm_gbs, "fma_peak_tfma": fma_peak / 1e12, "peak_kind": f"of {peak_kind}",
-        "traffic": NCU_TRAFFIC_BYTES.get(dominant) if (B, N, Ls, K) == tuple(HEADLINE[k] for k in "BNLK") else None,
+        "traffic": NCU_TRAFFIC_BYTES.get(dominant)
+        if (B, N, Ls, K) == tuple(HEADLINE[k] for k in "BNLK") and args.storage == "f32" else None,
         "algorithmic_bytes_per_launch": dk["algorithmic_bytes"], "avg_launch_ms": dk["ms"],
         "step_roofline_ms": step_roof * 1e3, "step_frac_of_roofline": step_roof / (ms_per_step * 1e-3),
         "note": "limiter is the shared-memory gather pipe (128 B/clk/SM, one gathered operand per FMA), not HBM",
@@ -704,9 +713,10 @@ def run_ours(args):
         line = {
             "metric": "FFI fwd+bwd samples/sec", "value": value, "unit": "samples/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32" if args.storage == "f32" else "bf16 storage, f32 accumulation",
             "data": "synthetic",
-            "config": dict(workload_config(B, N, L, K, world), launch="the rank's kernels of a step replayed as one CUDA graph, then the exchange" if graphed else "kernel by kernel",
+            "config": dict(workload_config(B, N, L, K, world, args.storage), launch="the rank's kernels of a step replayed as one CUDA graph, then the exchange" if graphed else "kernel by kernel",
                            **({"collective": {"resident": {"peer": "ffi_peer_sum", "nccl": "NCCL all-reduce",
                                                            "multimem": "in-switch (NVLS) all-reduce of torch symmetric memory"
                                                            }[resident_mode],
