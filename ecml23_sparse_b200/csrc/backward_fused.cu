@@ -815,7 +815,16 @@ __global__ void __launch_bounds__(THREADS, 1)
                     for (int off = 16; off >= LG; off /= 2) out[m] += __shfl_xor_sync(0xffffffffu, out[m], off);  // the groups
                 }
                 if (i < N && grp == 0) {
-                    float* dst = p.partial + ((static_cast<size_t>(r) * p.S + seg) * N + i) * p.Bpad + 4 * q;
+                    // One partial per range: the first segment stores, the later ones add to what this lane
+                    // stored before (a handful of fp32 additions of segment sums; the long sums stay inside
+                    // the segments, and the ranges are added in fp64 afterwards).
+                    float* dst = p.partial + (static_cast<size_t>(r) * N + i) * p.Bpad + 4 * q;
+                    if (seg > 0) {
+                        const float4 a = *reinterpret_cast<const float4*>(dst);
+                        const float4 b = *reinterpret_cast<const float4*>(dst + BT / 2);
+                        out[0] += a.x, out[1] += a.y, out[2] += a.z, out[3] += a.w;
+                        out[4] += b.x, out[5] += b.y, out[6] += b.z, out[7] += b.w;
+                    }
                     *reinterpret_cast<float4*>(dst) = make_float4(out[0], out[1], out[2], out[3]);
                     *reinterpret_cast<float4*>(dst + BT / 2) = make_float4(out[4], out[5], out[6], out[7]);
                 }
@@ -824,12 +833,12 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
     }
 
-    // Segments a range never reached hold zeros (ranges differ by at most one chunk).
-    for (int seg = static_cast<int>((c_end - c_begin + p.segChunks - 1) / p.segChunks); seg < p.S; ++seg) {
+    // A range without chunks still owns a partial: zeros.
+    if (c_begin >= c_end) {
         for (int j = 0; j < NI; ++j) {
             const int i = i_lo + warp * NI + j;
             if (i < N && grp == 0) {
-                float* dst = p.partial + ((static_cast<size_t>(r) * p.S + seg) * N + i) * p.Bpad + 4 * q;
+                float* dst = p.partial + (static_cast<size_t>(r) * N + i) * p.Bpad + 4 * q;
                 *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                 *reinterpret_cast<float4*>(dst + BT / 2) = make_float4(0.f, 0.f, 0.f, 0.f);
             }
@@ -873,7 +882,8 @@ bool fused_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, FusedC
     int seg = static_cast<int>(256.0 / (per_chunk > 1.0 ? per_chunk : 1.0));
     if (seg < 1) seg = 1;
     c->segChunks = seg;
-    c->S = static_cast<int>(ceil_div(ceil_div(plan->n_chunks, R), seg));
+    // the group kernel adds its segments into one partial per range; the register kernel keeps one per segment
+    c->S = group_kernel ? 1 : static_cast<int>(ceil_div(ceil_div(plan->n_chunks, R), seg));
     const int stat = width <= 128 ? 0 : (width <= 256 ? 1 : 2);
     const size_t cap = static_cast<size_t>((plan->max_slice_entries[stat] + 7) / 8 * 8 + 8);
     const size_t T = static_cast<size_t>(plan->chunk_rows);
