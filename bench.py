@@ -310,6 +310,59 @@ def extra_records(torch, ops, synth, ffi, dev, flush, hbm_gbs, fma_peak):
             out.append({"name": name, "error": repr(exc)})
         torch.cuda.empty_cache()
 
+    # The stacked configurations as whole training steps through the ops: FFI (ReLU) -> FFI with the loss fused into
+    # the output layer's forward, backward through both layers, optionally one Adam step on both weight arrays.
+    def stack_record(name, B, N0, N1, L, K1, K2, bf16, adam):
+        try:
+            store = torch.bfloat16 if bf16 else torch.float32
+            rpb = lambda n: max(64, min(32768, (1 << 28) // n))
+            x0T = synth.normal(SEED, 20, (N0, B), device=dev).to(store)
+            idx1 = synth.indices_without_replacement(SEED, 21, N1, K1, N0, device=dev, rows_per_block=rpb(N0))
+            W1 = synth.normal(SEED, 22, (N1, K1), std=(2.0 / K1) ** 0.5, device=dev).to(store)
+            idx2 = synth.indices_without_replacement(SEED, 23, L, K2, N1, device=dev, rows_per_block=rpb(N1))
+            W2 = synth.normal(SEED, 24, (L, K2), std=(2.0 / K2) ** 0.5, device=dev).to(store)
+            bias2 = torch.zeros(L, device=dev)
+            rp, lab = synth.multi_hot_targets(SEED, 25, B, L)
+            rp, lab = rp.to(dev), lab.to(dev)
+            plan1, plan2 = ffi.FFIPlan(idx1, N0), ffi.FFIPlan(idx2, N1)
+            opt = ffi.FusedAdam([W1.view(-1), W2.view(-1)], lr=1e-3) if adam else None
+
+            def step():
+                h_pre = ops._forward(x0T, idx1, W1, None, True)                                  # [B, N1] fp32
+                h = torch.relu(h_pre).to(store)
+                loss, gT = ops.forward_bce(h, idx2, W2, bias2, rp, lab, False)
+                gh, gW2, gb2 = ops._backward(h, idx2, W2, gT, False, plan=plan2, want_bias_grad=True,
+                                             grad_is_transposed=True)
+                gh_pre = gh * (h_pre > 0)
+                gx0, gW1, _ = ops._backward(x0T, idx1, W1, gh_pre, True, plan=plan1)
+                if opt is not None:
+                    opt.step([gW1.view(-1), gW2.view(-1)])
+                return loss
+
+            t_step = time_call(step, reps=5)
+            e = 2 if bf16 else 4
+            fma = 3 * B * (N1 * K1 + L * K2)
+            by = sum(algorithmic_bytes(B, n, l, k, e)[p] for n, l, k in ((N0, N1, K1), (N1, L, K2))
+                     for p in ("forward", "grad_w", "grad_x")) - 2 * 4 * B * L  # logits and g never reach HBM
+            roof = max(by / (hbm_gbs * 1e9), fma / fma_peak)
+            plan1.close()
+            plan2.close()
+            return {"name": name, "shape": {"B": B, "layers": [[N0, N1, K1], [N1, L, K2]], "storage": "bf16" if bf16 else "f32",
+                                            "adam": adam},
+                    "ms_per_step": t_step, "samples_per_s": B / (t_step * 1e-3), "step_roofline_ms": roof * 1e3,
+                    "frac": roof / (t_step * 1e-3),
+                    "note": "forward of both layers, sigmoid-BCE fused into the output layer, backward of both, ReLU and its "
+                            "mask as torch elementwise ops on the [B, hidden] activations"}
+        except Exception as exc:  # noqa: BLE001
+            return {"name": name, "error": repr(exc)}
+
+    out.append(stack_record("config 1: 768 -> 32,768 (K=32, ReLU) -> 670,091 (K=32), B=128, fp32, fused BCE",
+                            128, 768, 32_768, H["L"], 32, 32, False, False))
+    torch.cuda.empty_cache()
+    out.append(stack_record("config 2: 512 -> 65,536 (K=64, ReLU) -> 501,070 (K=32), B=256, bf16 storage, fused BCE + Adam",
+                            256, 512, 65_536, 501_070, 64, 32, True, True))
+    torch.cuda.empty_cache()
+
     # fused Adam on the headline layer's weights: 28 bytes per weight (w, m, v read + written, grad read)
     try:
         n = H["L"] * H["K"]
