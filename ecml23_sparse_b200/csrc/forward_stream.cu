@@ -108,7 +108,18 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_pair_kernel(FwdStreamPara
     float* wi = region;
     float* ys = region + 8 * K;
 
-    {
+    if (p.ldx % 4 == 0 && b0 + BT <= p.B && reinterpret_cast<uintptr_t>(p.xT) % 16 == 0) {
+        // whole tile inside the batch, rows 16-byte aligned: 16-byte loads and stores
+        constexpr int VR = BT / 4;
+        const int total = p.N * VR;
+#pragma unroll 4
+        for (int e = tid; e < total; e += kThreads) {
+            const int i = e / VR;
+            const int v = e - i * VR;
+            reinterpret_cast<float4*>(x_s)[e] =
+                __ldg(reinterpret_cast<const float4*>(p.xT + static_cast<size_t>(i) * p.ldx + b0) + v);
+        }
+    } else {
         const int total = p.N * BT;
 #pragma unroll 8
         for (int e = tid; e < total; e += kThreads) {
