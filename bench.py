@@ -618,28 +618,75 @@ def run_ours(args):
         gx_host = torch.empty((B, N)).pin_memory()
         loss_host = torch.empty(()).pin_memory()
 
-        def step_e2e():
+        # grad_x and the loss travel together: one buffer of N*B + 4 floats per rank (a slot of the symmetric
+        # allocation where there is one), one exchange per step
+        e2e_mode = resident_mode if world > 1 else "none"
+        pack_local = torch.zeros(N * B + 4, device=dev)
+
+        def e2e_buffer():
+            if e2e_mode == "multimem":
+                return peer.buf[0]
+            if e2e_mode == "peer":
+                return peer.slot()
+            return pack_local
+
+        def compute_e2e():
+            """Host -> device copies and this rank's kernels; leaves (grad_x partial, loss share) in the buffer."""
             x_dev.copy_(x_host, non_blocking=True)
             rp_dev.copy_(rp_host, non_blocking=True)
             lab_dev.copy_(lab_host, non_blocking=True)
             # logits never reach HBM: the forward kernel's epilogue writes the BCE gradient, transposed
             loss, gT = ops.forward_bce(x_dev, idx, W, bias, rp_dev, lab_dev, False, total_labels=L, label_offset=lo)
-            if peer is not None:
-                slot = peer.slot()
-                slot[N * B:N * B + 1].copy_(loss.view(1))
-                _, gW, gb = ops._backward(x_dev, idx, W, gT, False, plan=plan, want_bias_grad=True,
-                                          grad_is_transposed=True, feature_grad_out=slot[:N * B])
-                total = peer.sum(peer_out)
-                gx, loss = total[:N * B].view(B, N), total[N * B]
-            else:
-                gx, gW, gb = ops._backward(x_dev, idx, W, gT, False, plan=plan, want_bias_grad=True,
-                                           grad_is_transposed=True)
-                if world > 1:
-                    dist.all_reduce(gx)
-                    dist.all_reduce(loss)
+            buf = e2e_buffer()
+            buf[N * B:N * B + 1].copy_(loss.view(1))
+            ops._backward(x_dev, idx, W, gT, False, plan=plan, want_bias_grad=True, grad_is_transposed=True,
+                          feature_grad_out=buf[:N * B])
+            return buf
+
+        def finish_e2e(buf):
+            """Exchange between the ranks, then the device -> host copies of grad_x and the loss."""
+            if e2e_mode == "multimem":
+                torch.ops.symm_mem.multimem_all_reduce_(buf, "sum", dist.group.WORLD.group_name)
+            elif e2e_mode == "peer":
+                buf = peer.sum(peer_out)
+            elif e2e_mode == "nccl":
+                dist.all_reduce(buf)
+            gx, loss = buf[:N * B].view(B, N), buf[N * B]
             gx_host.copy_(gx, non_blocking=True)
             loss_host.copy_(loss, non_blocking=True)
             return gx, loss
+
+        def step_e2e_eager():
+            return finish_e2e(compute_e2e())
+
+        # as in the resident leg: the copies in and the rank's kernels replayed as one CUDA graph, the exchange and
+        # the copies out launched after it (not in ffi_peer_sum's mode, whose slots alternate)
+        step_e2e, e2e_graph = step_e2e_eager, None
+        if not args.no_graph and e2e_mode != "peer":
+            ok = torch.ones(1, device=dev)
+            try:
+                side = torch.cuda.Stream(device=dev)
+                side.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(side):
+                    for _ in range(2):
+                        compute_e2e()
+                torch.cuda.current_stream(dev).wait_stream(side)
+                torch.cuda.synchronize()
+                e2e_graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(e2e_graph):
+                    e2e_buf = compute_e2e()
+                torch.cuda.synchronize()
+            except Exception as exc:  # noqa: BLE001 - capture is an optimisation: fall back to plain launches
+                print(f"bench: CUDA graph capture of the e2e step failed on rank {rank}: {exc!r}", file=sys.stderr, flush=True)
+                ok.zero_()
+            if world > 1:
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if ok.item() == 1:
+                def step_e2e():
+                    e2e_graph.replay()
+                    return finish_e2e(e2e_buf)
+            else:
+                e2e_graph = None
 
         def e2e_partials():
             """This rank's grad_x partial and loss share of the same step, without any exchange."""
@@ -661,7 +708,10 @@ def run_ours(args):
             "ms_per_step": e2e_ms / args.steps, "ms_per_step_reps": e2e_reps,
             "path": "pinned host x[B,N] + CSR targets -> FanInSparseMatmul(+bias) with fused sigmoid-BCE gradient -> "
                     "FanInSparseMatmulGrad (grad_x, grad_W, grad_bias) -> loss and grad_x to host",
+            "launch": "copies in and the rank's kernels replayed as one CUDA graph, then exchange and copies out"
+                      if e2e_graph is not None else "call by call",
         }
+        e2e_graph = None
 
     # ---- per-kernel times for the roofline (rank-local, each call timed alone) -------------
     def time_call(fn, reps=20):
@@ -773,8 +823,8 @@ def run_ours(args):
                            **({"collective": {"resident": {"peer": "ffi_peer_sum", "nccl": "NCCL all-reduce",
                                                            "multimem": "in-switch (NVLS) all-reduce of torch symmetric memory"
                                                            }[resident_mode],
-                                              "e2e": "ffi_peer_sum (grad_x + loss, one launch)" if peer is not None
-                                              else "NCCL all-reduce"}} if world > 1 else {})),
+                                              "e2e": "the same exchange, grad_x and the loss in one buffer"}}
+                              if world > 1 else {})),
             "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
             "roofline": roofline, "cpu_baseline": cpu_baseline,
             "reps": {"count": max(1, args.reps), "ms_per_step": resident_reps, "reported": "median repetition"},
