@@ -662,27 +662,44 @@ extern "C" int ffi_forward_topk(const void* x, const int32_t* idx, const void* W
         return fail(FFI_ERR_INVALID_ARGUMENT, "NULL tensor passed to ffi_forward_topk");
     int rc = check_shape(B, N, L, K);
     if (rc != FFI_OK) return rc;
-    if (dtype != FFI_F32) return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_topk: dtype %d not supported", dtype);
+    if (dtype != FFI_F32 && dtype != FFI_BF16)
+        return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_topk: dtype %d not supported", dtype);
     if (label_offset < 0 || label_offset + L >= (1LL << 31))
         return fail(FFI_ERR_INVALID_ARGUMENT, "label_offset + L must fit 31 bits");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const size_t need = ffi_forward_topk_workspace_bytes(B, N, L, K, x_transposed, dtype);
     if (!workspace || reinterpret_cast<uintptr_t>(workspace) % kAlign != 0 || workspace_bytes < need)
         return fail(FFI_ERR_WORKSPACE, "ffi_forward_topk needs %zu bytes of %zu-byte aligned workspace", need, kAlign);
+    const bool bf16 = dtype == FFI_BF16;
+    if (bf16 && !bf16_takes_tiled_forward(B, N, K)) {
+        // narrow inputs in bf16 storage: widened (exactly) into the workspace, then the fp32 kernels
+        const float *x32 = nullptr, *W32 = nullptr;
+        void* rest = nullptr;
+        size_t rest_bytes = 0;
+        rc = widen_inputs(x, W, B, N, L, K, workspace, workspace_bytes, stream, &x32, &W32, &rest, &rest_bytes);
+        if (rc != FFI_OK) return rc;
+        return ffi_forward_topk(x32, idx, W32, bias, top_val, top_idx, k, B, N, L, K, label_offset, x_transposed, FFI_F32,
+                                rest, rest_bytes, stream_v);
+    }
     unsigned char* ws = static_cast<unsigned char*>(workspace);
     void* lists = ws;
-    float* xws = reinterpret_cast<float*>(ws + align_up(forward_topk_workspace_bytes(B)));
+    void* xws = ws + align_up(forward_topk_workspace_bytes(B));
 
     const bool smem = forward_uses_smem_x(static_cast<int>(B), static_cast<int>(N), static_cast<int>(K), nullptr);
     const XPlan xp = plan_x(smem, B, N, x_transposed);
-    const float* xT = nullptr;
-    rc = stage_x(xp, static_cast<const float*>(x), xws, B, N, x_transposed, stream, &xT);
-    if (rc != FFI_OK) return rc;
     FwdArgs a;
-    a.xT = xT;
+    if (bf16) {
+        rc = stage_x_any(xp, x, xws, B, N, x_transposed, 2, stream, &a.xT);
+    } else {
+        const float* xT = nullptr;
+        rc = stage_x(xp, static_cast<const float*>(x), static_cast<float*>(xws), B, N, x_transposed, stream, &xT);
+        a.xT = xT;
+    }
+    if (rc != FFI_OK) return rc;
     a.ldx = xp.ld;
     a.idx = idx;
-    a.W = static_cast<const float*>(W);
+    a.W = W;
+    a.bf16 = bf16;
     a.bias = bias;
     a.y = nullptr;
     a.B = static_cast<int>(B);
@@ -692,9 +709,7 @@ extern "C" int ffi_forward_topk(const void* x, const int32_t* idx, const void* W
     bool handled = false;
     rc = launch_forward_topk_stream(a, lists, top_val, top_idx, k, static_cast<int>(label_offset), stream, &handled);
     if (rc != FFI_OK) return rc;
-    if (!handled)
-        return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_topk covers K %% 4 == 0 with x resident in shared memory; "
-                                         "use ffi_forward and a top-k over y for this shape");
+    if (!handled) return fail(FFI_ERR_UNSUPPORTED, "ffi_forward_topk: no kernel takes this shape");
     return FFI_OK;
 }
 

@@ -108,6 +108,27 @@ __device__ __forceinline__ typename Vec<BPL>::type load_lane_vec(const __nv_bflo
 // ---- launchers implemented in the .cu files ---------------------------------------
 // xT is x in [N][ldx] layout (batch contiguous); xT and W are fp32, or bf16 when `bf16` is set (only the
 // tiled kernels take bf16; the callers see to that).
+// Top-k epilogues of the forward kernels (evaluation: P@1, P@3, P@5 need 5 candidates per sample).
+constexpr int kTopK = 8;  // capacity of a top-k list
+
+// Sorted (value descending, row ascending) insertion; `better` orders candidates the way
+// tf.nn.top_k does: higher value first, lower index on ties.
+__device__ __forceinline__ bool topk_better(float v, int i, float v2, int i2) { return v > v2 || (v == v2 && i < i2); }
+__device__ __forceinline__ void topk_insert(float (&tv)[kTopK], int (&ti)[kTopK], float v, int i) {
+    if (!topk_better(v, i, tv[kTopK - 1], ti[kTopK - 1])) return;
+    tv[kTopK - 1] = v;
+    ti[kTopK - 1] = i;
+#pragma unroll
+    for (int j = kTopK - 1; j >= 1; --j) {
+        if (topk_better(tv[j], ti[j], tv[j - 1], ti[j - 1])) {
+            const float fv = tv[j];
+            const int fi = ti[j];
+            tv[j] = tv[j - 1], ti[j] = ti[j - 1];
+            tv[j - 1] = fv, ti[j - 1] = fi;
+        }
+    }
+}
+
 struct FwdArgs {
     const void* xT;
     int64_t ldx;

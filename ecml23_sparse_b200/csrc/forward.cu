@@ -45,6 +45,9 @@ struct FwdKernelParams {
     float scale;
     double* loss_partials;
     int loss_kind;
+    // top-k epilogue (MODE 2): thread (part, batch element) keeps the kTopK best logits of the rows
+    // part, part + PARTS, ... of every tile of its CTA; lists [batch tile][cta][part][batch][kTopK] of (value, row)
+    uint2* topk_lists;
 };
 
 // loss and d(loss)/dz of one logit whose target is 0 (ffi_loss_kind: BCE, squared hinge, hinge)
@@ -64,9 +67,12 @@ __device__ __forceinline__ void loss_for_negative(int kind, float z, float& valu
 // TX: storage type of x and W.  bf16 values are widened where they are loaded (the x tile and the staged W
 // rows in shared memory are fp32; x gathered from global memory is widened in registers), so the
 // arithmetic is that of the fp32 kernel on exactly the same values, at half the gather traffic.
-template <int BPL, bool XSMEM, bool LOSS, typename TX>
+// MODE 0 writes y, 1 the loss gradient (see FwdKernelParams), 2 the top-k lists.
+template <int BPL, bool XSMEM, int MODE, typename TX>
 __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_kernel(FwdKernelParams p) {
     constexpr int BT = 32 * BPL;
+    constexpr bool LOSS = MODE == 1;
+    constexpr int PARTS = kThreads / BT;  // top-k: threads per batch element
     constexpr bool kBf16 = !std::is_same<TX, float>::value;
     const TX* xT = static_cast<const TX*>(p.xT);
     const TX* Wt = static_cast<const TX*>(p.W);
@@ -141,8 +147,18 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_kernel(FwdKernelParams p)
 
     // Coalesced write-out of a finished tile: one warp per batch row, lanes along o.
     float loss_local = 0.f;
+    const int tk_bl = tid % BT, tk_part = tid / BT;
+    float tv[kTopK];
+    int ti[kTopK];
+#pragma unroll
+    for (int j = 0; j < kTopK; ++j) tv[j] = -INFINITY, ti[j] = 0x7fffffff;
     auto write_out = [&](long long o0, const float* ys) {
-        if constexpr (LOSS) {
+        if constexpr (MODE == 2) {
+            const int rows = min(TO, static_cast<int>(L - o0));
+            if (b0 + tk_bl < p.B)
+                for (int c = tk_part; c < rows; c += PARTS)
+                    topk_insert(tv, ti, ys[c * (BT + 1) + tk_bl], static_cast<int>(o0) + c);
+        } else if constexpr (LOSS) {
             // one warp per output row, lanes along the batch: gT rows are batch-contiguous
             const bool last_bt = blockIdx.y + 1 == gridDim.y;
             const int cols = last_bt ? static_cast<int>(p.ldg) - b0 : BT;  // the last tile also clears the padding
@@ -238,6 +254,15 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_kernel(FwdKernelParams p)
     __pipeline_wait_prior(0);
     __syncthreads();
     if (prev_o0 >= 0) write_out(prev_o0, y_s + (buf ^ 1) * TO * (BT + 1));
+    if constexpr (MODE == 2) {
+        if (b0 + tk_bl < p.B) {
+            uint2* out = p.topk_lists +
+                         ((static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * PARTS + tk_part) * (BT * kTopK) +
+                         tk_bl * kTopK;
+#pragma unroll
+            for (int j = 0; j < kTopK; ++j) out[j] = make_uint2(__float_as_uint(tv[j]), static_cast<unsigned>(ti[j]));
+        }
+    }
     if constexpr (LOSS) {
         double v = static_cast<double>(loss_local);
 #pragma unroll
@@ -295,15 +320,17 @@ int pick_TO(size_t budget, int N, int bpl, bool xsmem, int Kp) {
 
 constexpr int kMaxLossPartialsTile = 1024;  // doubles the caller's scratch holds for the per-CTA loss sums
 
-template <int BPL, bool XSMEM, bool LOSS, typename TX>
+template <int BPL, bool XSMEM, int MODE, typename TX>
 int launch_fwd_t(const FwdKernelParams& p, size_t smem, int nBT, const DeviceInfo& dev,
                  cudaStream_t stream, int* ctas_out) {
-    auto kern = ffi_fwd_kernel<BPL, XSMEM, LOSS, TX>;
+    constexpr bool LOSS = MODE == 1;
+    auto kern = ffi_fwd_kernel<BPL, XSMEM, MODE, TX>;
     FFI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(smem)));
     int occ = 0;
     FFI_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kThreads, smem));
     if (occ < 1) return fail(FFI_ERR_CUDA, "forward kernel does not fit on an SM (smem %zu)", smem);
+    if (MODE == 2) occ = 1;  // the scratch for the top-k lists is sized for one CTA per SM
     int per_bt = dev.sm_count * occ / nBT;
     if (per_bt < 1) per_bt = 1;
     dim3 grid(static_cast<unsigned>(min(p.numTiles, per_bt)), static_cast<unsigned>(nBT));
@@ -316,7 +343,7 @@ int launch_fwd_t(const FwdKernelParams& p, size_t smem, int nBT, const DeviceInf
     return FFI_OK;
 }
 
-template <bool LOSS, typename TX>
+template <int LOSS, typename TX>
 int launch_fwd_tile(const FwdKernelParams& p, size_t smem, int nBT, int bpl, bool xsmem, const DeviceInfo& dev,
                     cudaStream_t stream, int* ctas_out) {
     if (xsmem) {
@@ -360,8 +387,14 @@ struct TileLossEpilogue {
     int loss_kind;
     int* ctas;
 };
+struct TileTopkEpilogue {
+    uint2* lists;
+    int* lists_per_tile;  // out: CTAs per batch tile x threads per batch element
+    int* bt;              // out: batch tile width
+};
 
-static int launch_forward_tile(const FwdArgs& a, const TileLossEpilogue* loss, cudaStream_t stream) {
+static int launch_forward_tile(const FwdArgs& a, const TileLossEpilogue* loss, const TileTopkEpilogue* topk,
+                               cudaStream_t stream) {
     DeviceInfo dev;
     int rc = get_device_info(&dev);
     if (rc != FFI_OK) return rc;
@@ -384,6 +417,7 @@ static int launch_forward_tile(const FwdArgs& a, const TileLossEpilogue* loss, c
     p.scale = loss ? loss->scale : 0.f;
     p.loss_partials = loss ? loss->loss_partials : nullptr;
     p.loss_kind = loss ? loss->loss_kind : 0;
+    p.topk_lists = topk ? topk->lists : nullptr;
 
     int bpl = 1;
     const bool xsmem = forward_uses_smem_x(a.B, a.N, a.K, &bpl);
@@ -398,12 +432,20 @@ static int launch_forward_tile(const FwdArgs& a, const TileLossEpilogue* loss, c
             reinterpret_cast<uintptr_t>(a.xT) % 16 != 0)
             return fail(FFI_ERR_INVALID_ARGUMENT, "wide-N forward needs a padded, aligned x copy");
     }
-    if (a.bf16) {
-        if (loss) return launch_fwd_tile<true, __nv_bfloat16>(p, smem, nBT, bpl, xsmem, dev, stream, loss->ctas);
-        return launch_fwd_tile<false, __nv_bfloat16>(p, smem, nBT, bpl, xsmem, dev, stream, nullptr);
+    if (topk) {
+        int ctas = 0;
+        rc = a.bf16 ? launch_fwd_tile<2, __nv_bfloat16>(p, smem, nBT, bpl, xsmem, dev, stream, &ctas)
+                    : launch_fwd_tile<2, float>(p, smem, nBT, bpl, xsmem, dev, stream, &ctas);
+        *topk->bt = 32 * bpl;
+        *topk->lists_per_tile = ctas / nBT * (kThreads / (32 * bpl));
+        return rc;
     }
-    if (loss) return launch_fwd_tile<true, float>(p, smem, nBT, bpl, xsmem, dev, stream, loss->ctas);
-    return launch_fwd_tile<false, float>(p, smem, nBT, bpl, xsmem, dev, stream, nullptr);
+    if (a.bf16) {
+        if (loss) return launch_fwd_tile<1, __nv_bfloat16>(p, smem, nBT, bpl, xsmem, dev, stream, loss->ctas);
+        return launch_fwd_tile<0, __nv_bfloat16>(p, smem, nBT, bpl, xsmem, dev, stream, nullptr);
+    }
+    if (loss) return launch_fwd_tile<1, float>(p, smem, nBT, bpl, xsmem, dev, stream, loss->ctas);
+    return launch_fwd_tile<0, float>(p, smem, nBT, bpl, xsmem, dev, stream, nullptr);
 }
 
 int launch_forward(const FwdArgs& a, cudaStream_t stream) {
@@ -413,7 +455,7 @@ int launch_forward(const FwdArgs& a, cudaStream_t stream) {
         int rc = launch_forward_stream(a, stream, &handled);
         if (rc != FFI_OK || handled) return rc;
     }
-    return launch_forward_tile(a, nullptr, stream);
+    return launch_forward_tile(a, nullptr, nullptr, stream);
 }
 
 // Forward with the loss gradient in the epilogue for the shapes the barrier-free kernel does not take
@@ -421,7 +463,14 @@ int launch_forward(const FwdArgs& a, cudaStream_t stream) {
 int launch_forward_loss_tile(const FwdArgs& a, float* gT, int64_t ldg, float scale, double* loss_partials, int* ctas,
                              int loss_kind, cudaStream_t stream) {
     TileLossEpilogue e{gT, ldg, scale, loss_partials, loss_kind, ctas};
-    return launch_forward_tile(a, &e, stream);
+    return launch_forward_tile(a, &e, nullptr, stream);
+}
+
+// Forward with the top-k epilogue for those shapes (and for bf16 storage): fills `lists` as
+// [batch tile][*lists_per_tile][*bt][kTopK] for the merge kernel of forward_stream.cu.
+int launch_forward_topk_tile(const FwdArgs& a, void* lists, int* lists_per_tile, int* bt, cudaStream_t stream) {
+    TileTopkEpilogue e{static_cast<uint2*>(lists), lists_per_tile, bt};
+    return launch_forward_tile(a, nullptr, &e, stream);
 }
 
 int launch_transpose_pad(const float* src, float* dst, int rows, int cols, int64_t ld_dst,

@@ -36,26 +36,7 @@ struct FwdStreamParams {
     uint2* topk_lists;
 };
 
-constexpr int kTopK = 8;  // capacity of a top-k list (P@1, P@3, P@5 need 5)
 constexpr size_t kMaxLossPartials = 1024;  // doubles the caller's scratch holds for the per-CTA loss sums
-
-// Sorted (value descending, row ascending) insertion; `better` orders candidates the way
-// tf.nn.top_k does: higher value first, lower index on ties.
-__device__ __forceinline__ bool topk_better(float v, int i, float v2, int i2) { return v > v2 || (v == v2 && i < i2); }
-__device__ __forceinline__ void topk_insert(float (&tv)[kTopK], int (&ti)[kTopK], float v, int i) {
-    if (!topk_better(v, i, tv[kTopK - 1], ti[kTopK - 1])) return;
-    tv[kTopK - 1] = v;
-    ti[kTopK - 1] = i;
-#pragma unroll
-    for (int j = kTopK - 1; j >= 1; --j) {
-        if (topk_better(tv[j], ti[j], tv[j - 1], ti[j - 1])) {
-            const float fv = tv[j];
-            const int fi = ti[j];
-            tv[j] = tv[j - 1], ti[j] = ti[j - 1];
-            tv[j - 1] = fv, ti[j - 1] = fi;
-        }
-    }
-}
 
 // loss and d(loss)/dz of one logit whose target is 0
 __device__ __forceinline__ void loss_negative(int kind, float z, float& value, float& grad) {
@@ -470,6 +451,8 @@ int launch_forward_bce_stream(const FwdArgs& a, float* gT, int64_t ldg, float sc
     return launch_forward_stream_impl(a, &e, nullptr, stream, handled);
 }
 
+int launch_forward_topk_tile(const FwdArgs& a, void* lists, int* lists_per_tile, int* bt, cudaStream_t stream);
+
 // Scratch for the warp lists of forward_topk: an upper bound over the grids the launcher may choose.
 size_t forward_topk_workspace_bytes(int64_t B) {
     DeviceInfo dev;
@@ -487,8 +470,14 @@ int launch_forward_topk_stream(const FwdArgs& a, void* scratch, float* top_val, 
     int ctas_x = 0, bt = 0;
     TopkEpilogue e{static_cast<uint2*>(scratch), &ctas_x, &bt};
     int rc = launch_forward_stream_impl(a, nullptr, &e, stream, handled);
-    if (rc != FFI_OK || !*handled) return rc;
-    topk_merge_kernel<<<static_cast<unsigned>(a.B), 256, 0, stream>>>(static_cast<const uint2*>(scratch), ctas_x * kWarps,
+    if (rc != FFI_OK) return rc;
+    int lists_per_tile = ctas_x * kWarps;
+    if (!*handled) {  // wide inputs, K not a multiple of 4, bf16 storage: the CTA-tile kernel's top-k epilogue
+        rc = launch_forward_topk_tile(a, scratch, &lists_per_tile, &bt, stream);
+        if (rc != FFI_OK) return rc;
+        *handled = true;
+    }
+    topk_merge_kernel<<<static_cast<unsigned>(a.B), 256, 0, stream>>>(static_cast<const uint2*>(scratch), lists_per_tile,
                                                                       bt, a.B, kk, label_offset, top_val, top_idx);
     FFI_LAUNCH_CHECK("topk_merge_kernel");
     return FFI_OK;

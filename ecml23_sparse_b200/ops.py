@@ -292,22 +292,23 @@ def forward_topk(features, lookup, weights, bias, k: int, transposed: bool, labe
     of tf.nn.top_k, without materialising the logits: what PrecisionAtK (sparse/metrics.py:9-70)
     consumes.  With a sharded label dimension call it per shard (`label_offset` = first label of the
     shard) and merge the candidates with `merge_topk`."""
-    features = _check_cuda("features", features, (torch.float32,))
-    weights = _check_cuda("weights", weights, (torch.float32,))
+    features = _check_cuda("features", features, (torch.float32, torch.bfloat16))
+    weights = _check_cuda("weights", weights, (features.dtype,))
     lookup = _as_index(lookup)
     B, N, L, K = _shapes(features, lookup, weights, transposed)
     dev = features.device
     lib = _lib.load()
+    dtype = _lib.FFI_BF16 if features.dtype == torch.bfloat16 else _lib.FFI_F32
     top_val = torch.empty((B, k), dtype=torch.float32, device=dev)
     top_idx = torch.empty((B, k), dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
-        ws_bytes = lib.ffi_forward_topk_workspace_bytes(B, N, L, K, int(transposed), _lib.FFI_F32)
+        ws_bytes = lib.ffi_forward_topk_workspace_bytes(B, N, L, K, int(transposed), dtype)
         ws = _workspace(dev, ws_bytes + 256)
         off = (-ws.data_ptr()) % 256
         _lib.check(lib.ffi_forward_topk(features.data_ptr(), lookup.data_ptr(), weights.data_ptr(),
                                         bias.data_ptr() if bias is not None else None, top_val.data_ptr(),
                                         top_idx.data_ptr(), k, B, N, L, K, label_offset, int(transposed),
-                                        _lib.FFI_F32, ws.data_ptr() + off, ws.numel() - off, _stream_ptr(dev)))
+                                        dtype, ws.data_ptr() + off, ws.numel() - off, _stream_ptr(dev)))
     return top_val, top_idx
 
 

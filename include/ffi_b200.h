@@ -243,8 +243,9 @@ int ffi_grad_x_static(const float* W, const float* gT, int64_t ldg, const ffi_pl
  * tf.nn.top_k (value descending, lower index first on ties).  It is what PrecisionAtK
  * (sparse/metrics.py:9-70: topk_as_matrix + the overlap with the true labels) needs from the
  * B x L logits, which here never reach HBM; with a sharded label dimension every shard returns
- * its own k candidates.  Covers K % 4 == 0 with the x tile resident in shared memory
- * (FFI_ERR_UNSUPPORTED otherwise: use ffi_forward and a top-k over y there).
+ * its own k candidates.  Every shape ffi_forward takes is covered, fp32 and bf16 storage: the
+ * barrier-free kernel where the x tile is resident in shared memory and K % 4 == 0, the CTA-tile
+ * kernel (wide inputs gathered from L2, any K, bf16 read directly) elsewhere.
  */
 size_t ffi_forward_topk_workspace_bytes(int64_t B, int64_t N, int64_t L, int64_t K, int x_transposed,
                                         int dtype);

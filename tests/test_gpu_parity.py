@@ -579,7 +579,10 @@ def test_fused_forward_hinge_losses(cuda_device, shape, transposed, loss_name):
 
 
 @pytest.mark.parametrize("shape,transposed", [((128, 768, 20_011, 32), True), ((37, 254, 513, 16), False),
-                                              ((64, 100, 7, 8), True)], ids=["headline-like", "small", "few-rows"])
+                                              ((64, 100, 7, 8), True), ((128, 32_768, 5_003, 32), False),
+                                              ((33, 40_000, 2_000, 72), True), ((70, 300, 1_500, 7), False),
+                                              ((200, 500, 900, 5), True)],
+                         ids=["headline-like", "small", "few-rows", "wide-N", "wide-N-K72", "odd-K", "odd-K-two-batch-tiles"])
 def test_fused_forward_topk_and_precision_at_k(cuda_device, shape, transposed):
     """Top-k of the logits from the forward kernel's epilogue (the logits are never written) against a
     stable sort of the oracle's logits; P@k as the reference's PrecisionAtK accumulates it."""
@@ -689,3 +692,11 @@ def test_bf16_storage_of_x_and_w(cuda_device, shape, transposed):
     assert abs(float(loss) - loss_ref) <= 2e-5 * abs(loss_ref) + 1e-7
     assert_close(gT[:, :B].t().cpu().numpy(), g_ref, 5e-5, 2e-7 / (B * L), "fused BCE gradient on bf16 storage")
     assert not gT[:, B:].any()
+    # top-k on bf16 storage: values of the oracle's logits on the rounded inputs, every label carries its logit
+    k = 5
+    vals, lab = ops.forward_topk(xin, to_cuda(idx, dev), Wb.to(dev), to_cuda(bias, dev), k, transposed)
+    z64 = oracle.forward_f64(xr, idx, Wr, bias=bias)
+    want = -np.sort(-z64, axis=1)[:, :k]
+    assert_close(vals.cpu().numpy(), want, RTOL, ATOL, "bf16 top-k values")
+    assert_close(vals.cpu().numpy(), np.take_along_axis(z64, lab.cpu().numpy().astype(np.int64), axis=1), RTOL, ATOL,
+                 "bf16 top-k: value of label")
