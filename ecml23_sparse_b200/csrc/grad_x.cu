@@ -340,19 +340,23 @@ bool narrow_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, Narro
 }
 
 // g [B][L] -> gT [L][ldg] (zero padded batch), optionally with grad_bias[o] = sum_b g[b,o].
-// One block owns 64 outputs and walks the whole batch in slabs of 128, so the column sums are
+// One block owns `tro` <= 64 outputs and walks the whole batch in slabs of 128, so the column sums are
 // complete inside the block and are added in a fixed order.  Rows of g start at arbitrary 4-byte
 // offsets (L is odd in practice), so a 256-byte row segment costs one extra 32-byte sector.
-constexpr int kTrO = 64;   // outputs per block
-__global__ void __launch_bounds__(256, 4) transpose_g_kernel(const float* __restrict__ g, float* __restrict__ gT,
-                                                          float* __restrict__ gbias, int B, long long L,
-                                                          long long ldg) {
+// The launcher picks `tro` so that the blocks fill a whole number of waves over the GPU: with 64 outputs
+// per block a short L (a shard of the label dimension) leaves the last wave nearly empty.
+constexpr int kTrO = 64;        // most outputs per block
+constexpr int kTrResident = 4;  // blocks per SM (launch bound)
+__global__ void __launch_bounds__(256, kTrResident) transpose_g_kernel(const float* __restrict__ g, float* __restrict__ gT,
+                                                                    float* __restrict__ gbias, int B, long long L,
+                                                                    long long ldg, int tro) {
     __shared__ float tile[128][kTrO + 1];
     const int tid = threadIdx.x;
     const int tx = tid & (kTrO - 1), ty = tid / kTrO;  // load: tx = output, ty = batch row within a group of 4
     const int bx = tid & 127, oy0 = tid >> 7;           // store: bx = batch column, oy0 = first output row
-    const long long o0 = static_cast<long long>(blockIdx.x) * kTrO;
-    const bool ocol = o0 + tx < L;
+    const long long o0 = static_cast<long long>(blockIdx.x) * tro;
+    const int nrows = static_cast<int>(L - o0 < tro ? L - o0 : tro);  // outputs of this block
+    const bool ocol = tx < nrows;
     float colsum = 0.f;
     for (long long bb = 0; bb < ldg; bb += 128) {
         const float* src = g + static_cast<size_t>(bb + ty) * L + o0 + tx;
@@ -365,11 +369,9 @@ __global__ void __launch_bounds__(256, 4) transpose_g_kernel(const float* __rest
         }
         __syncthreads();
         if (bb + bx < ldg) {
-#pragma unroll
-            for (int u = 0; u < kTrO / 2; ++u) {
-                const int oy = oy0 + 2 * u;
-                if (o0 + oy < L) gT[static_cast<size_t>(o0 + oy) * ldg + bb + bx] = tile[bx][oy];
-            }
+            float* dst = gT + static_cast<size_t>(o0) * ldg + bb + bx;
+#pragma unroll 8
+            for (int oy = oy0; oy < nrows; oy += 2) dst[static_cast<size_t>(oy) * ldg] = tile[bx][oy];
         }
         __syncthreads();
     }
@@ -390,9 +392,17 @@ __global__ void __launch_bounds__(256, 4) transpose_g_kernel(const float* __rest
 int64_t transposed_g_stride(int64_t B) { return B <= 32 ? 32 : (B <= 64 ? 64 : round_up(B, 128)); }
 
 int launch_transpose_g(const float* g, float* gT, float* gbias, int B, int64_t L, int64_t ldg, cudaStream_t stream) {
-    const long long blocks_o = ceil_div(L, kTrO);
+    DeviceInfo dev;
+    const int rc = get_device_info(&dev);
+    if (rc != FFI_OK) return rc;
+    // the fewest waves that blocks of kTrO outputs need, then the narrowest blocks that still fit those waves
+    const long long slots = static_cast<long long>(dev.sm_count) * kTrResident;
+    const long long waves = ceil_div(ceil_div(L, kTrO), slots);
+    long long tro = ceil_div(L, slots * waves);
+    tro = tro < 8 ? 8 : (tro > kTrO ? kTrO : tro);
+    const long long blocks_o = ceil_div(L, tro);
     if (blocks_o > 2147483647LL) return fail(FFI_ERR_UNSUPPORTED, "L too large");
-    transpose_g_kernel<<<static_cast<unsigned>(blocks_o), 256, 0, stream>>>(g, gT, gbias, B, L, ldg);
+    transpose_g_kernel<<<static_cast<unsigned>(blocks_o), 256, 0, stream>>>(g, gT, gbias, B, L, ldg, static_cast<int>(tro));
     FFI_LAUNCH_CHECK("transpose_g_kernel");
     return FFI_OK;
 }
