@@ -89,29 +89,6 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_pair_kernel(FwdStreamPara
     float* wi = region;
     float* ys = region + 8 * K;
 
-    if (p.ldx % 4 == 0 && b0 + BT <= p.B && reinterpret_cast<uintptr_t>(p.xT) % 16 == 0) {
-        // whole tile inside the batch, rows 16-byte aligned: 16-byte loads and stores
-        constexpr int VR = BT / 4;
-        const int total = p.N * VR;
-#pragma unroll 4
-        for (int e = tid; e < total; e += kThreads) {
-            const int i = e / VR;
-            const int v = e - i * VR;
-            reinterpret_cast<float4*>(x_s)[e] =
-                __ldg(reinterpret_cast<const float4*>(p.xT + static_cast<size_t>(i) * p.ldx + b0) + v);
-        }
-    } else {
-        const int total = p.N * BT;
-#pragma unroll 8
-        for (int e = tid; e < total; e += kThreads) {
-            const int i = e / BT;
-            const int bl = e - i * BT;
-            const int b = b0 + bl;
-            x_s[e] = b < p.B ? p.xT[static_cast<size_t>(i) * p.ldx + b] : 0.f;
-        }
-    }
-    __syncthreads();
-
     const float* xs_lane = x_s + (VPL == 8 ? 4 : VPL) * q;
     const long long numQuads = (static_cast<long long>(L) + 3) / 4;
     const long long gw = static_cast<long long>(blockIdx.x) * kWarps + warp;
@@ -136,8 +113,33 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_pair_kernel(FwdStreamPara
         __pipeline_commit();
     };
 
+    // the warp's first W/idx rows are requested before the x tile is filled: both trips to memory overlap
     long long qd = gw;
     if (qd < numQuads) issue(2 * qd, 0);
+
+    if (p.ldx % 4 == 0 && b0 + BT <= p.B && reinterpret_cast<uintptr_t>(p.xT) % 16 == 0) {
+        // whole tile inside the batch, rows 16-byte aligned: 16-byte loads and stores
+        constexpr int VR = BT / 4;
+        const int total = p.N * VR;
+#pragma unroll 12
+        for (int e = tid; e < total; e += kThreads) {
+            const int i = e / VR;
+            const int v = e - i * VR;
+            reinterpret_cast<float4*>(x_s)[e] =
+                __ldg(reinterpret_cast<const float4*>(p.xT + static_cast<size_t>(i) * p.ldx + b0) + v);
+        }
+    } else {
+        const int total = p.N * BT;
+#pragma unroll 8
+        for (int e = tid; e < total; e += kThreads) {
+            const int i = e / BT;
+            const int bl = e - i * BT;
+            const int b = b0 + bl;
+            x_s[e] = b < p.B ? p.xT[static_cast<size_t>(i) * p.ldx + b] : 0.f;
+        }
+    }
+    __syncthreads();
+
     int s = 0;
     float loss_local = 0.f;
     // top-k mode: lane keeps the lists of batch columns lane, lane + 32, ... of the tile
