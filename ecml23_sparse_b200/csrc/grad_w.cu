@@ -330,6 +330,7 @@ bool grad_w_uses_smem_x(int B, int N, int K, int* bpl_out) {
 }
 
 int launch_grad_w_stream(const GradWArgs& a, cudaStream_t stream, bool* handled);
+int launch_grad_w_gather(const GradWArgs& a, int bpl, cudaStream_t stream, bool* handled);
 
 int launch_grad_w(const GradWArgs& a, cudaStream_t stream) {
     DeviceInfo dev;
@@ -364,6 +365,12 @@ int launch_grad_w(const GradWArgs& a, cudaStream_t stream) {
 
     int bpl = 1;
     const bool xsmem = grad_w_uses_smem_x(a.B, a.N, a.K, &bpl);
+    if (!xsmem) {
+        // wide inputs: the per-warp gather kernel where the transposed gradient and aligned rows allow it
+        bool handled = false;
+        rc = launch_grad_w_gather(a, bpl, stream, &handled);
+        if (rc != FFI_OK || handled) return rc;
+    }
     p.TO = gw_pick_TO(dev.max_smem_optin, a.N, bpl, xsmem, p.Kp);
     if (p.TO < 16) return fail(FFI_ERR_UNSUPPORTED, "fan-in K=%d too large for the staged tiles", a.K);
     p.numTiles = static_cast<int>(ceil_div(a.L, p.TO));
