@@ -108,6 +108,23 @@ __device__ __forceinline__ typename Vec<BPL>::type load_lane_vec(const __nv_bflo
 // ---- launchers implemented in the .cu files ---------------------------------------
 // xT is x in [N][ldx] layout (batch contiguous); xT and W are fp32, or bf16 when `bf16` is set (only the
 // tiled kernels take bf16; the callers see to that).
+// loss and d(loss)/dz of one logit whose target is 0 (ffi_loss_kind: BCE, squared hinge, hinge);
+// shared by the loss epilogues of all forward kernels, so that they agree bit for bit
+__device__ __forceinline__ void loss_for_negative(int kind, float z, float& value, float& grad) {
+    if (kind == 0) {
+        // one exponential serves both: s = exp(-|z|), softplus(z) = max(z,0) + log(1+s),
+        // sigmoid(z) = 1/(1+s) or s/(1+s); hardware approximations (a few ulp) are well inside 1e-5
+        const float s = __expf(-fabsf(z));
+        const float r = __fdividef(1.f, 1.f + s);
+        value = fmaxf(z, 0.f) + __logf(1.f + s);
+        grad = z >= 0.f ? r : s * r;
+    } else {
+        const float h = fmaxf(1.f + z, 0.f);
+        value = kind == 1 ? h * h : h;
+        grad = kind == 1 ? 2.f * h : (h > 0.f ? 1.f : 0.f);
+    }
+}
+
 // Top-k epilogues of the forward kernels (evaluation: P@1, P@3, P@5 need 5 candidates per sample).
 constexpr int kTopK = 8;  // capacity of a top-k list
 

@@ -50,20 +50,6 @@ struct FwdKernelParams {
     uint2* topk_lists;
 };
 
-// loss and d(loss)/dz of one logit whose target is 0 (ffi_loss_kind: BCE, squared hinge, hinge)
-__device__ __forceinline__ void loss_for_negative(int kind, float z, float& value, float& grad) {
-    if (kind == 0) {
-        const float s = __expf(-fabsf(z));
-        const float r = __fdividef(1.f, 1.f + s);
-        value = fmaxf(z, 0.f) + __logf(1.f + s);
-        grad = z >= 0.f ? r : s * r;
-    } else {
-        const float h = fmaxf(1.f + z, 0.f);
-        value = kind == 1 ? h * h : h;
-        grad = kind == 1 ? 2.f * h : (h > 0.f ? 1.f : 0.f);
-    }
-}
-
 // TX: storage type of x and W.  bf16 values are widened where they are loaded (the x tile and the staged W
 // rows in shared memory are fp32; x gathered from global memory is widened in registers), so the
 // arithmetic is that of the fp32 kernel on exactly the same values, at half the gather traffic.
@@ -376,6 +362,8 @@ bool forward_uses_smem_x(int B, int N, int K, int* bpl_out) {
 }
 
 int launch_forward_stream(const FwdArgs& a, cudaStream_t stream, bool* handled);
+int launch_forward_gather(const FwdArgs& a, int bpl, float* gT, int64_t ldg, float scale, double* loss_partials,
+                          int loss_kind, int max_partials, int* ctas, cudaStream_t stream, bool* handled);
 
 // The CTA-tile kernel (any K, unaligned rows, x gathered from L2 when its tile does not fit shared memory);
 // with `loss` set it writes the loss gradient instead of y (see FwdKernelParams).
@@ -421,6 +409,14 @@ static int launch_forward_tile(const FwdArgs& a, const TileLossEpilogue* loss, c
 
     int bpl = 1;
     const bool xsmem = forward_uses_smem_x(a.B, a.N, a.K, &bpl);
+    if (!xsmem && !topk) {
+        // wide inputs: the per-warp gather kernel where fan-in and alignment allow it
+        bool handled = false;
+        rc = launch_forward_gather(a, bpl, loss ? loss->gT : nullptr, loss ? loss->ldg : 0, loss ? loss->scale : 0.f,
+                                   loss ? loss->loss_partials : nullptr, loss ? loss->loss_kind : 0, kMaxLossPartialsTile,
+                                   loss ? loss->ctas : nullptr, stream, &handled);
+        if (rc != FFI_OK || handled) return rc;
+    }
     p.TO = pick_TO(dev.max_smem_optin, a.N, bpl, xsmem, p.Kp);
     if (p.TO < 16) return fail(FFI_ERR_UNSUPPORTED, "fan-in K=%d too large for the staged tiles", a.K);
     p.numTiles = static_cast<int>(ceil_div(a.L, p.TO));

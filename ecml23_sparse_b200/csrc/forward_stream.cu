@@ -38,22 +38,6 @@ struct FwdStreamParams {
 
 constexpr size_t kMaxLossPartials = 1024;  // doubles the caller's scratch holds for the per-CTA loss sums
 
-// loss and d(loss)/dz of one logit whose target is 0
-__device__ __forceinline__ void loss_negative(int kind, float z, float& value, float& grad) {
-    if (kind == 0) {
-        // one exponential serves both: s = exp(-|z|), softplus(z) = max(z,0) + log(1+s),
-        // sigmoid(z) = 1/(1+s) or s/(1+s); hardware approximations (a few ulp) are well inside 1e-5
-        const float s = __expf(-fabsf(z));
-        const float r = __fdividef(1.f, 1.f + s);
-        value = fmaxf(z, 0.f) + __logf(1.f + s);
-        grad = z >= 0.f ? r : s * r;
-    } else {
-        const float h = fmaxf(1.f + z, 0.f);
-        value = kind == 1 ? h * h : h;
-        grad = kind == 1 ? 2.f * h : (h > 0.f ? 1.f : 0.f);
-    }
-}
-
 // A HALF warp covers the batch tile (16 lanes x VPL batch elements) and the two halves of a warp
 // work on the two rows of a row pair at once.  The fetch of a row's W and idx values is then one
 // shared-memory access for both rows (two addresses, one per half) instead of a warp-uniform access
@@ -214,7 +198,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffi_fwd_pair_kernel(FwdStreamPara
                         for (int j = 0; j < W4; ++j) {
                             const bool live = b + j < p.B;
                             float v, g;
-                            loss_negative(p.loss_kind, acc[j0 + j] + bias, v, g);
+                            loss_for_negative(p.loss_kind, acc[j0 + j] + bias, v, g);
                             if (live && mine) loss_local += v;
                             gv[j] = live ? p.scale * g : 0.f;
                         }
