@@ -74,11 +74,20 @@ template <>
 struct Vec<4> {
     using type = float4;
 };
+template <>
+struct Vec<8> {
+    using type = uint4;  // eight bf16 values, still packed (bf16 storage only)
+};
 
 __device__ __forceinline__ float vec_get(const float& v, int) { return v; }
 __device__ __forceinline__ float vec_get(const float2& v, int j) { return j == 0 ? v.x : v.y; }
 __device__ __forceinline__ float vec_get(const float4& v, int j) {
     return j == 0 ? v.x : (j == 1 ? v.y : (j == 2 ? v.z : v.w));
+}
+
+__device__ __forceinline__ float vec_get(const uint4& v, int j) {
+    const unsigned word = j < 2 ? v.x : (j < 4 ? v.y : (j < 6 ? v.z : v.w));
+    return (j & 1) ? __uint_as_float(word & 0xffff0000u) : __uint_as_float(word << 16);
 }
 
 // ---- storage types of x and W: fp32 or bf16 (a bf16 value widens to fp32 exactly) ----------------
@@ -94,7 +103,9 @@ __device__ __forceinline__ typename Vec<BPL>::type load_lane_vec(const float* ba
 }
 template <int BPL>
 __device__ __forceinline__ typename Vec<BPL>::type load_lane_vec(const __nv_bfloat16* base, size_t v) {
-    if constexpr (BPL == 4) {
+    if constexpr (BPL == 8) {
+        return __ldg(reinterpret_cast<const uint4*>(base) + v);
+    } else if constexpr (BPL == 4) {
         const uint2 r = __ldg(reinterpret_cast<const uint2*>(base) + v);
         return make_float4(bf16_lo(r.x), bf16_hi(r.x), bf16_lo(r.y), bf16_hi(r.y));
     } else if constexpr (BPL == 2) {
@@ -102,6 +113,35 @@ __device__ __forceinline__ typename Vec<BPL>::type load_lane_vec(const __nv_bflo
         return make_float2(bf16_lo(r), bf16_hi(r));
     } else {
         return __bfloat162float(base[v]);
+    }
+}
+
+// BPL consecutive fp32 values at base + lane * BPL (16-byte aligned rows)
+template <int BPL>
+__device__ __forceinline__ void load_lane_f32(const float* base, int lane, float (&out)[BPL]) {
+    if constexpr (BPL >= 4) {
+#pragma unroll
+        for (int c = 0; c < BPL / 4; ++c) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(base) + lane * (BPL / 4) + c);
+            out[4 * c] = t.x, out[4 * c + 1] = t.y, out[4 * c + 2] = t.z, out[4 * c + 3] = t.w;
+        }
+    } else if constexpr (BPL == 2) {
+        const float2 t = __ldg(reinterpret_cast<const float2*>(base) + lane);
+        out[0] = t.x, out[1] = t.y;
+    } else {
+        out[0] = __ldg(base + lane);
+    }
+}
+template <int BPL>
+__device__ __forceinline__ void store_lane_f32(float* base, int lane, const float (&v)[BPL]) {
+    if constexpr (BPL >= 4) {
+#pragma unroll
+        for (int c = 0; c < BPL / 4; ++c)
+            reinterpret_cast<float4*>(base)[lane * (BPL / 4) + c] = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+    } else if constexpr (BPL == 2) {
+        reinterpret_cast<float2*>(base)[lane] = make_float2(v[0], v[1]);
+    } else {
+        base[lane] = v[0];
     }
 }
 

@@ -143,18 +143,12 @@ __global__ void __launch_bounds__(kThreads, 2) ffi_fwd_gather_kernel(FwdGatherPa
                         gv[j] = b < p.B ? p.scale * g : 0.f;
                     }
                     // the stored row is ldg wide (a multiple of BPL): the columns past B receive zeros
-                    if (b0 + lane * BPL < p.ldg) {
-                        float* dst = p.gT + static_cast<size_t>(o) * p.ldg + b0 + lane * BPL;
-                        if constexpr (BPL == 4) *reinterpret_cast<float4*>(dst) = make_float4(gv[0], gv[1], gv[2], gv[3]);
-                        else if constexpr (BPL == 2) *reinterpret_cast<float2*>(dst) = make_float2(gv[0], gv[1]);
-                        else *dst = gv[0];
-                    }
+                    if (b0 + lane * BPL < p.ldg) store_lane_f32<BPL>(p.gT + static_cast<size_t>(o) * p.ldg + b0, lane, gv);
                 } else {
-                    float* dst = ys + r * S + lane * BPL;
-                    if constexpr (BPL == 4)
-                        *reinterpret_cast<float4*>(dst) = make_float4(acc[0] + bias, acc[1] + bias, acc[2] + bias, acc[3] + bias);
-                    else if constexpr (BPL == 2) *reinterpret_cast<float2*>(dst) = make_float2(acc[0] + bias, acc[1] + bias);
-                    else *dst = acc[0] + bias;
+                    float out[BPL];
+#pragma unroll
+                    for (int j = 0; j < BPL; ++j) out[j] = acc[j] + bias;
+                    store_lane_f32<BPL>(ys + r * S, lane, out);
                 }
             }
             __syncwarp();
@@ -231,6 +225,9 @@ int launch_forward_gather(const FwdArgs& a, int bpl, float* gT, int64_t ldg, flo
     DeviceInfo dev;
     int rc = get_device_info(&dev);
     if (rc != FFI_OK) return rc;
+    // bf16 storage with the loss epilogue: eight batch elements per lane (one 16-byte gather covers 256 batch
+    // columns per warp, W and idx are streamed once per 256 instead of once per 128) where the rows are padded to it
+    if (a.bf16 && gT && bpl == 4 && a.B > 128 && a.ldx % 256 == 0 && ldg % 256 == 0) bpl = 8;
     const int BT = 32 * bpl;
     const int nBT = static_cast<int>(ceil_div(a.B, BT));
     const int kq = a.bf16 ? 8 : 4;
@@ -257,6 +254,7 @@ int launch_forward_gather(const FwdArgs& a, int bpl, float* gT, int64_t ldg, flo
     p.loss_partials = loss_partials;
     p.loss_kind = loss_kind;
     *handled = true;
+    if (bpl == 8) return launch_fwd_gather_t<8, 1, __nv_bfloat16>(p, nBT, max_partials, dev, stream, ctas);
     if (a.bf16) {
         if (gT) return launch_fwd_gather_b<1, __nv_bfloat16>(p, bpl, nBT, max_partials, dev, stream, ctas);
         return launch_fwd_gather_b<0, __nv_bfloat16>(p, bpl, nBT, max_partials, dev, stream, ctas);

@@ -67,11 +67,12 @@ __global__ void __launch_bounds__(kThreads, 2) ffi_grad_w_gather_kernel(GatherPa
     for (int s = 0; o < L; o += GW, s ^= 1) {
         issue(o + GW, s ^ 1);
         // this lane's g values of the row
-        const V gv = load_lane_vec<BPL>(p.gT + static_cast<size_t>(o) * p.ldg + p.b0, static_cast<size_t>(lane));
+        float gv[BPL];
+        load_lane_f32<BPL>(p.gT + static_cast<size_t>(o) * p.ldg + p.b0, lane, gv);
         if (p.gbias) {
             float gsum = 0.f;
 #pragma unroll
-            for (int j = 0; j < BPL; ++j) gsum += vec_get(gv, j);
+            for (int j = 0; j < BPL; ++j) gsum += gv[j];
 #pragma unroll
             for (int off = 16; off >= 1; off /= 2) gsum += __shfl_xor_sync(0xffffffffu, gsum, off);
             if (lane == 0) {
@@ -96,7 +97,7 @@ __global__ void __launch_bounds__(kThreads, 2) ffi_grad_w_gather_kernel(GatherPa
                 for (int u = 0; u < 8; ++u) {
                     float a = 0.f;
 #pragma unroll
-                    for (int j = 0; j < BPL; ++j) a = fmaf(vec_get(gv, j), vec_get(v[u], j), a);
+                    for (int j = 0; j < BPL; ++j) a = fmaf(gv[j], vec_get(v[u], j), a);
                     dbuf[(k + u) * kRow + lane] = a;
                 }
             }
@@ -110,7 +111,7 @@ __global__ void __launch_bounds__(kThreads, 2) ffi_grad_w_gather_kernel(GatherPa
                 for (int u = 0; u < 4; ++u) {
                     float a = 0.f;
 #pragma unroll
-                    for (int j = 0; j < BPL; ++j) a = fmaf(vec_get(gv, j), vec_get(v[u], j), a);
+                    for (int j = 0; j < BPL; ++j) a = fmaf(gv[j], vec_get(v[u], j), a);
                     dbuf[(k + u) * kRow + lane] = a;
                 }
             }
@@ -166,6 +167,9 @@ int launch_grad_w_gather(const GradWArgs& a, int bpl, cudaStream_t stream, bool*
     DeviceInfo dev;
     int rc = get_device_info(&dev);
     if (rc != FFI_OK) return rc;
+    // bf16 x: eight batch elements per lane (one 16-byte gather covers 256 batch columns per warp) where the
+    // batch is that wide and the rows are padded to it
+    if (a.bf16 && bpl == 4 && a.B > 128 && a.ldx % 256 == 0 && a.ldg % 256 == 0) bpl = 8;
     const int BT = 32 * bpl;
     const int nBT = static_cast<int>(ceil_div(a.B, BT));
     if (!a.gT || a.K % 4 != 0 || reinterpret_cast<uintptr_t>(a.idx) % 16 != 0 || a.ldg % 4 != 0 ||
@@ -190,6 +194,7 @@ int launch_grad_w_gather(const GradWArgs& a, int bpl, cudaStream_t stream, bool*
     p.accumulate = 0;
     *handled = true;
     if (a.bf16) {
+        if (bpl == 8) return launch_gather_t<8, __nv_bfloat16>(p, nBT, dev, stream);
         if (bpl == 4) return launch_gather_t<4, __nv_bfloat16>(p, nBT, dev, stream);
         if (bpl == 2) return launch_gather_t<2, __nv_bfloat16>(p, nBT, dev, stream);
         return launch_gather_t<1, __nv_bfloat16>(p, nBT, dev, stream);

@@ -654,8 +654,11 @@ def test_fused_forward_loss_on_tiled_kernel_shapes(cuda_device, shape, loss_name
 
 @pytest.mark.parametrize("shape,transposed", [((64, 512, 3_001, 32), True), ((37, 254, 513, 16), False),
                                               ((130, 100, 600, 73), False), ((128, 768, 20_011, 32), True),
-                                              ((100, 300, 2_001, 64), False), ((128, 32_768, 1_001, 32), True)],
-                         ids=["wiki-like", "small", "odd", "headline-like", "K64-staged-x", "wide"])
+                                              ((100, 300, 2_001, 64), False), ((128, 32_768, 1_001, 32), True),
+                                              ((256, 40_000, 1_501, 32), True), ((300, 33_000, 777, 64), False),
+                                              ((512, 34_000, 515, 72), False)],
+                         ids=["wiki-like", "small", "odd", "headline-like", "K64-staged-x", "wide", "wide-B256",
+                              "wide-B300", "wide-B512-K72"])
 def test_bf16_storage_of_x_and_w(cuda_device, shape, transposed):
     """x and W stored as bf16, fp32 accumulation (benchmark configurations 2-4; the reference is fp32
     only, tfsparse/cc/kernels/register.cpp:79-109).  Inputs are rounded to bf16 once; the CUDA result
