@@ -103,7 +103,9 @@ def test_extra_shapes(cuda_device, shape, transposed):
     check_against_oracle(cuda_device, x, idx, W, g, transposed, size_id(shape))
 
 
-@pytest.mark.parametrize("shape", [(16, 5000, 3000, 8), (130, 3000, 2000, 16), (40, 2500, 1500, 7)], ids=size_id)
+@pytest.mark.parametrize("shape", [(16, 5000, 3000, 8), (130, 3000, 2000, 16), (40, 2500, 1500, 7), (1, 60_000, 5, 4),
+                                   (33, 7_000, 9, 36), (129, 2_500, 41, 8), (64, 3_300, 1_001, 72), (257, 1_200, 300, 12)],
+                         ids=size_id)
 @pytest.mark.parametrize("transposed", [False, True], ids=["plain", "tp"])
 def test_wide_inputs(cuda_device, shape, transposed):
     # N too large for the shared-memory x tile / register accumulators: the global-memory paths
