@@ -20,7 +20,11 @@ namespace {
 
 constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
-constexpr int kRows = 8;  // rows of results a warp collects before it writes y
+// rows of results a warp collects before it writes y (fewer for the widest lanes, whose rows are twice as long)
+template <int BPL>
+struct ResultRows {
+    static constexpr int value = BPL == 8 ? 4 : 8;
+};
 
 struct FwdGatherParams {
     const void* xT;  // [N][ldx], element type TX
@@ -43,6 +47,7 @@ template <int BPL, int MODE, typename TX>
 __global__ void __launch_bounds__(kThreads, 2) ffi_fwd_gather_kernel(FwdGatherParams p) {
     constexpr int BT = 32 * BPL;
     constexpr int S = BT + 4;  // row stride of the result tile
+    constexpr int kRows = ResultRows<BPL>::value;
     constexpr bool kBf16 = !std::is_same<TX, float>::value;
     constexpr int WPE = kBf16 ? 2 : 1;  // weights per 32-bit word of a staged W row
     using V = typename Vec<BPL>::type;
@@ -154,7 +159,7 @@ __global__ void __launch_bounds__(kThreads, 2) ffi_fwd_gather_kernel(FwdGatherPa
             __syncwarp();
         }
         if constexpr (MODE == 0) {
-            // eight consecutive lanes write the eight outputs of one batch row: 32-byte runs along o
+            // kRows consecutive lanes write the kRows outputs of one batch row: 32- or 16-byte runs along o
             const int rows = static_cast<int>(L - o0 < kRows ? L - o0 : kRows);
             const int oo = lane & (kRows - 1);
 #pragma unroll 4
@@ -185,6 +190,7 @@ template <int BPL, int MODE, typename TX>
 int launch_fwd_gather_t(const FwdGatherParams& p, int nBT, int max_partials, const DeviceInfo& dev, cudaStream_t stream,
                         int* ctas_out) {
     constexpr int BT = 32 * BPL;
+    constexpr int kRows = ResultRows<BPL>::value;
     constexpr int WPE = std::is_same<TX, float>::value ? 1 : 2;
     auto kern = ffi_fwd_gather_kernel<BPL, MODE, TX>;
     const size_t warpWords = 2 * static_cast<size_t>(p.K / WPE + p.K) + (MODE == 0 ? kRows * (BT + 4) : 0);
@@ -225,9 +231,9 @@ int launch_forward_gather(const FwdArgs& a, int bpl, float* gT, int64_t ldg, flo
     DeviceInfo dev;
     int rc = get_device_info(&dev);
     if (rc != FFI_OK) return rc;
-    // bf16 storage with the loss epilogue: eight batch elements per lane (one 16-byte gather covers 256 batch
+    // bf16 storage: eight batch elements per lane (one 16-byte gather covers 256 batch
     // columns per warp, W and idx are streamed once per 256 instead of once per 128) where the rows are padded to it
-    if (a.bf16 && gT && bpl == 4 && a.B > 128 && a.ldx % 256 == 0 && ldg % 256 == 0) bpl = 8;
+    if (a.bf16 && bpl == 4 && a.B > 128 && a.ldx % 256 == 0 && (!gT || ldg % 256 == 0)) bpl = 8;
     const int BT = 32 * bpl;
     const int nBT = static_cast<int>(ceil_div(a.B, BT));
     const int kq = a.bf16 ? 8 : 4;
@@ -254,7 +260,10 @@ int launch_forward_gather(const FwdArgs& a, int bpl, float* gT, int64_t ldg, flo
     p.loss_partials = loss_partials;
     p.loss_kind = loss_kind;
     *handled = true;
-    if (bpl == 8) return launch_fwd_gather_t<8, 1, __nv_bfloat16>(p, nBT, max_partials, dev, stream, ctas);
+    if (bpl == 8) {
+        if (gT) return launch_fwd_gather_t<8, 1, __nv_bfloat16>(p, nBT, max_partials, dev, stream, ctas);
+        return launch_fwd_gather_t<8, 0, __nv_bfloat16>(p, nBT, max_partials, dev, stream, ctas);
+    }
     if (a.bf16) {
         if (gT) return launch_fwd_gather_b<1, __nv_bfloat16>(p, bpl, nBT, max_partials, dev, stream, ctas);
         return launch_fwd_gather_b<0, __nv_bfloat16>(p, bpl, nBT, max_partials, dev, stream, ctas);
