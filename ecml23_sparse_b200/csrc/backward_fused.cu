@@ -511,6 +511,90 @@ __device__ __forceinline__ void tmem_store_sums(unsigned taddr, const Lane8& sum
         : "memory");
 }
 
+// The 4 batch elements one lane holds when a group of 8 lanes covers a batch of at most 32.
+struct Lane4 {
+    u64 a, b;
+    __device__ __forceinline__ void zero() { a = b = 0ull; }
+    // columns 4q..4q+3 at ptr: one 16-byte piece
+    template <int HALF>
+    __device__ __forceinline__ void load_shared(const unsigned char* ptr) {
+        const ulonglong2 t0 = *reinterpret_cast<const ulonglong2*>(ptr);
+        a = t0.x, b = t0.y;
+    }
+    __device__ __forceinline__ void axpy(float w, const Lane4& g) {
+        const u64 ww = pack2(w, w);
+        a = fma2(ww, g.a, a), b = fma2(ww, g.b, b);
+    }
+    __device__ __forceinline__ float dot(const Lane4& g) const {
+        float lo, hi;
+        unpack2(fma2(g.b, b, mul2(g.a, a)), lo, hi);
+        return lo + hi;
+    }
+    __device__ __forceinline__ float sum() const {
+        float f[4];
+        unpack2(a, f[0], f[1]), unpack2(b, f[2], f[3]);
+        return (f[0] + f[1]) + (f[2] + f[3]);
+    }
+};
+// 8 columns of this thread's TMEM lane -> (sums, x) of one input, complete on return
+__device__ __forceinline__ void tmem_load_input(unsigned taddr, Lane4& sums, Lane4& x) {
+    asm volatile(
+        "{\n"
+        ".reg .b32 t<8>;\n"
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {t0, t1, t2, t3, t4, t5, t6, t7}, [%4];\n"
+        "tcgen05.wait::ld.sync.aligned;\n"
+        "mov.b64 %0, {t0, t1};\n mov.b64 %1, {t2, t3};\n mov.b64 %2, {t4, t5};\n mov.b64 %3, {t6, t7};\n"
+        "}"
+        : "=l"(sums.a), "=l"(sums.b), "=l"(x.a), "=l"(x.b)
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_store_sums(unsigned taddr, const Lane4& sums) {
+    asm volatile(
+        "{\n"
+        ".reg .b32 t<4>;\n"
+        "mov.b64 {t0, t1}, %1;\n mov.b64 {t2, t3}, %2;\n"
+        "tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {t0, t1, t2, t3};\n"
+        "}" ::"r"(taddr),
+        "l"(sums.a), "l"(sums.b)
+        : "memory");
+}
+// VPL consecutive 32-bit columns of this thread's TMEM lane
+template <int VPL>
+__device__ __forceinline__ void tmem_store_cols(unsigned taddr, const unsigned (&r)[VPL]) {
+    if constexpr (VPL == 8) {
+        tmem_store8(taddr, r);
+    } else {
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+                     "r"(r[2]), "r"(r[3])
+                     : "memory");
+    }
+}
+// ... loaded and complete on return
+template <int VPL>
+__device__ __forceinline__ void tmem_load_cols(unsigned taddr, unsigned (&r)[VPL]) {
+    if constexpr (VPL == 8) {
+        unsigned dummy[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+        tmem_load8(taddr, r);
+        tmem_wait_load(r, dummy);
+    } else {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];\n"
+            "tcgen05.wait::ld.sync.aligned;"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+            : "r"(taddr)
+            : "memory");
+    }
+}
+template <int VPL>
+struct LaneOf {
+    using type = Lane8;
+};
+template <>
+struct LaneOf<4> {
+    using type = Lane4;
+};
+
 // G lane groups per warp: a group of 32/G lanes covers the BT = 256/G batch columns of one entry (8 per lane),
 // so a warp step works on G consecutive entries of a run.  G = 2 is the batch 65..128 case described above;
 // G = 4 covers batch <= 64 with a quarter of a warp per entry (a quarter warp reads one 128-byte half of a
@@ -521,18 +605,24 @@ __device__ __forceinline__ void tmem_store_sums(unsigned taddr, const Lane8& sum
 // into its fp32 bit pattern by the thread that fetched it once the copy has landed (the entry's code tells
 // which half: the chunk's first position is even, so the parity of the position within the chunk is the
 // parity of the flat position).
-template <int NI, int THREADS, int SLOTS, int G, typename TX>
+//
+// VPL = batch elements per lane: 8, or 4 for a batch of at most 32 (G = 4: eight lanes x 4 cover the 32 columns of
+// the tile with ONE 16-byte piece per lane; an input's state is 8 TMEM columns, so a warp owns 16 inputs, a CTA
+// 256, and three slices instead of six fetch each g tile).
+template <int NI, int THREADS, int SLOTS, int G, typename TX, int VPL = 8>
 __global__ void __launch_bounds__(THREADS, 1)
     ffi_bwd_pairs_kernel(BwdFusedParams p, const __grid_constant__ CUtensorMap g_map) {
     constexpr bool kBf16 = !std::is_same<TX, float>::value;
+    using LaneT = typename LaneOf<VPL>::type;
     const TX* xTt = static_cast<const TX*>(p.xT);
     constexpr int LG = 32 / G;    // lanes per group
-    constexpr int BT = 8 * LG;    // batch columns of the tile
-    constexpr int HALF = 2 * BT;  // bytes between a lane's two 16-byte pieces of a tile row
+    constexpr int BT = VPL * LG;  // batch columns of the tile
+    constexpr int HALF = 2 * BT;  // bytes between a lane's two 16-byte pieces of a tile row (VPL = 8)
+    constexpr int COLS = 2 * VPL; // TMEM columns of one input: its sums and its x values
     constexpr int kThreads = THREADS, kWarps = THREADS / 32, kSlots = SLOTS;  // shadow the file-wide values
     constexpr int CPN = kWarps * NI + 1;
     constexpr unsigned kRowMask = (1u << kKShift) - 1u;
-    static_assert((THREADS / 128) * NI * 16 <= kTmemCols, "the warps of a lane quarter share the TMEM columns");
+    static_assert((THREADS / 128) * NI * COLS <= kTmemCols, "the warps of a lane quarter share the TMEM columns");
     static_assert(SLOTS * G == 32, "the lane reduction maps the 32 lanes to (buffered step, group)");
     static_assert(32 + G <= kDRow, "a dot-buffer row holds 32 dots and G entry codes");
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -562,21 +652,36 @@ __global__ void __launch_bounds__(THREADS, 1)
     __syncthreads();
     tmem_fence_after_sync();
     const unsigned tmem_base = *tmem_base_p;
-    // lanes 32*(warp % 4) .. +31 are the ones this warp may touch; its inputs take NI*16 columns
+    // lanes 32*(warp % 4) .. +31 are the ones this warp may touch; its inputs take NI*COLS columns
     const unsigned taddr0 = tmem_base + ((static_cast<unsigned>(warp & 3) * 32u) << 16) +
-                            static_cast<unsigned>(warp >> 2) * (NI * 16);
+                            static_cast<unsigned>(warp >> 2) * (NI * COLS);
 
-    for (int j = 0; j < NI; ++j) {
-        const int i = i_lo + warp * NI + j;
-        unsigned xv[8], zero[8];
-#pragma unroll
-        for (int m = 0; m < 8; ++m) {
-            const int b = (m < 4 ? 0 : BT / 2) + 4 * q + (m & 3);
-            xv[m] = __float_as_uint((i < N && b < p.B) ? widen(xTt[static_cast<size_t>(i) * p.ldx + b]) : 0.f);
-            zero[m] = 0u;
+    if constexpr (VPL == 8) {
+        for (int j = 0; j < NI; ++j) {
+            const int i = i_lo + warp * NI + j;
+            unsigned xv[8], zero[8];
+    #pragma unroll
+            for (int m = 0; m < 8; ++m) {
+                const int b = (m < 4 ? 0 : BT / 2) + 4 * q + (m & 3);
+                xv[m] = __float_as_uint((i < N && b < p.B) ? widen(xTt[static_cast<size_t>(i) * p.ldx + b]) : 0.f);
+                zero[m] = 0u;
+            }
+            tmem_store8(taddr0 + j * 16, zero);
+            tmem_store8(taddr0 + j * 16 + 8, xv);
         }
-        tmem_store8(taddr0 + j * 16, zero);
-        tmem_store8(taddr0 + j * 16 + 8, xv);
+    } else {
+        for (int j = 0; j < NI; ++j) {
+            const int i = i_lo + warp * NI + j;
+            unsigned xv[VPL], zero[VPL];
+    #pragma unroll
+            for (int m = 0; m < VPL; ++m) {
+                const int b = (m < 4 ? 0 : BT / 2) + 4 * q + (m & 3);
+                xv[m] = __float_as_uint((i < N && b < p.B) ? widen(xTt[static_cast<size_t>(i) * p.ldx + b]) : 0.f);
+                zero[m] = 0u;
+            }
+            tmem_store_cols<VPL>(taddr0 + j * COLS, zero);
+            tmem_store_cols<VPL>(taddr0 + j * COLS + VPL, xv);
+        }
     }
     tmem_wait_store();
 
@@ -701,8 +806,8 @@ __global__ void __launch_bounds__(THREADS, 1)
         // grad_bias of the chunk's rows: the slices of a range take turns, each row is one group's sum
         if (p.gbias && static_cast<int>(c % gridDim.y) == static_cast<int>(blockIdx.y)) {
             for (int rr = G * warp + grp; rr < T; rr += G * kWarps) {
-                Lane8 v;
-                v.load_shared<HALF>(gs_lane + rr * (BT * 4));
+                LaneT v;
+                v.template load_shared<HALF>(gs_lane + rr * (BT * 4));
                 float sum = v.sum();
 #pragma unroll
                 for (int off = LG / 2; off >= 1; off /= 2) sum += __shfl_xor_sync(0xffffffffu, sum, off);
@@ -744,14 +849,14 @@ __global__ void __launch_bounds__(THREADS, 1)
         for (int j = 0; j < NI; ++j) {
             const int t = cp[j + 1];
             if (e >= t) continue;
-            Lane8 acc, xr;
-            tmem_load_input(taddr0 + j * 16, acc, xr);
+            LaneT acc, xr;
+            tmem_load_input(taddr0 + j * COLS, acc, xr);
             // two steps (2 G entries) per iteration: all loads are issued before the stores
             for (; e + 2 * G <= t; e += 2 * G) {
                 const uint2 en0 = ent[e], en1 = ent[e + G];
-                Lane8 g0, g1;
-                g0.load_shared<HALF>(gs_lane + (en0.y & kRowMask));
-                g1.load_shared<HALF>(gs_lane + (en1.y & kRowMask));
+                LaneT g0, g1;
+                g0.template load_shared<HALF>(gs_lane + (en0.y & kRowMask));
+                g1.template load_shared<HALF>(gs_lane + (en1.y & kRowMask));
                 if (dptr > dlast2) reduce_slots();
                 acc.axpy(__uint_as_float(en0.x), g0);
                 acc.axpy(__uint_as_float(en1.x), g1);
@@ -763,8 +868,8 @@ __global__ void __launch_bounds__(THREADS, 1)
             }
             if (e + G <= t) {
                 const uint2 en0 = ent[e];
-                Lane8 g0;
-                g0.load_shared<HALF>(gs_lane + (en0.y & kRowMask));
+                LaneT g0;
+                g0.template load_shared<HALF>(gs_lane + (en0.y & kRowMask));
                 if (dptr > dlast1) reduce_slots();
                 acc.axpy(__uint_as_float(en0.x), g0);
                 dptr[0] = xr.dot(g0);
@@ -774,11 +879,11 @@ __global__ void __launch_bounds__(THREADS, 1)
             }
             if (e < t) {  // the run's last step has entries for the first t - e groups only
                 uint2 en0 = make_uint2(0u, kPadCode);
-                Lane8 g0;
+                LaneT g0;
                 g0.zero();
                 if (grp < t - e) {
                     en0 = ent[e];
-                    g0.load_shared<HALF>(gs_lane + (en0.y & kRowMask));
+                    g0.template load_shared<HALF>(gs_lane + (en0.y & kRowMask));
                 }
                 if (dptr > dlast1) reduce_slots();
                 acc.axpy(__uint_as_float(en0.x), g0);
@@ -787,7 +892,7 @@ __global__ void __launch_bounds__(THREADS, 1)
                 dptr += kDRow;
                 e = t;
             }
-            tmem_store_sums(taddr0 + j * 16, acc);
+            tmem_store_sums(taddr0 + j * COLS, acc);
         }
         if (dptr != dlane) reduce_slots();
         tmem_wait_store();
@@ -799,34 +904,67 @@ __global__ void __launch_bounds__(THREADS, 1)
         const long long done = c - c_begin + 1;
         if (done % p.segChunks == 0 || c + 1 == c_end) {
             const int seg = static_cast<int>((done - 1) / p.segChunks);
-            for (int j = 0; j < NI; ++j) {
-                const int i = i_lo + warp * NI + j;
-                unsigned av[8], zero[8];
-                tmem_load8(taddr0 + j * 16, av);
-#pragma unroll
-                for (int m = 0; m < 8; ++m) zero[m] = 0u;
-                tmem_wait_load(av, zero);
-                tmem_store8(taddr0 + j * 16, zero);
-                float out[8];
-#pragma unroll
-                for (int m = 0; m < 8; ++m) {
-                    out[m] = __uint_as_float(av[m]);
-#pragma unroll
-                    for (int off = 16; off >= LG; off /= 2) out[m] += __shfl_xor_sync(0xffffffffu, out[m], off);  // the groups
-                }
-                if (i < N && grp == 0) {
-                    // One partial per range: the first segment stores, the later ones add to what this lane
-                    // stored before (a handful of fp32 additions of segment sums; the long sums stay inside
-                    // the segments, and the ranges are added in fp64 afterwards).
-                    float* dst = p.partial + (static_cast<size_t>(r) * N + i) * p.Bpad + 4 * q;
-                    if (seg > 0) {
-                        const float4 a = *reinterpret_cast<const float4*>(dst);
-                        const float4 b = *reinterpret_cast<const float4*>(dst + BT / 2);
-                        out[0] += a.x, out[1] += a.y, out[2] += a.z, out[3] += a.w;
-                        out[4] += b.x, out[5] += b.y, out[6] += b.z, out[7] += b.w;
+            if constexpr (VPL == 8) {
+                for (int j = 0; j < NI; ++j) {
+                    const int i = i_lo + warp * NI + j;
+                    unsigned av[8], zero[8];
+                    tmem_load8(taddr0 + j * 16, av);
+    #pragma unroll
+                    for (int m = 0; m < 8; ++m) zero[m] = 0u;
+                    tmem_wait_load(av, zero);
+                    tmem_store8(taddr0 + j * 16, zero);
+                    float out[8];
+    #pragma unroll
+                    for (int m = 0; m < 8; ++m) {
+                        out[m] = __uint_as_float(av[m]);
+    #pragma unroll
+                        for (int off = 16; off >= LG; off /= 2) out[m] += __shfl_xor_sync(0xffffffffu, out[m], off);  // the groups
                     }
-                    *reinterpret_cast<float4*>(dst) = make_float4(out[0], out[1], out[2], out[3]);
-                    *reinterpret_cast<float4*>(dst + BT / 2) = make_float4(out[4], out[5], out[6], out[7]);
+                    if (i < N && grp == 0) {
+                        // One partial per range: the first segment stores, the later ones add to what this lane
+                        // stored before (a handful of fp32 additions of segment sums; the long sums stay inside
+                        // the segments, and the ranges are added in fp64 afterwards).
+                        float* dst = p.partial + (static_cast<size_t>(r) * N + i) * p.Bpad + 4 * q;
+                        if (seg > 0) {
+                            const float4 a = *reinterpret_cast<const float4*>(dst);
+                            const float4 b = *reinterpret_cast<const float4*>(dst + BT / 2);
+                            out[0] += a.x, out[1] += a.y, out[2] += a.z, out[3] += a.w;
+                            out[4] += b.x, out[5] += b.y, out[6] += b.z, out[7] += b.w;
+                        }
+                        *reinterpret_cast<float4*>(dst) = make_float4(out[0], out[1], out[2], out[3]);
+                        *reinterpret_cast<float4*>(dst + BT / 2) = make_float4(out[4], out[5], out[6], out[7]);
+                    }
+                }
+            } else {
+                for (int j = 0; j < NI; ++j) {
+                    const int i = i_lo + warp * NI + j;
+                    unsigned av[VPL], zero[VPL];
+    #pragma unroll
+                    for (int m = 0; m < VPL; ++m) zero[m] = 0u;
+                    tmem_load_cols<VPL>(taddr0 + j * COLS, av);
+                    tmem_store_cols<VPL>(taddr0 + j * COLS, zero);
+                    float out[VPL];
+    #pragma unroll
+                    for (int m = 0; m < VPL; ++m) {
+                        out[m] = __uint_as_float(av[m]);
+    #pragma unroll
+                        for (int off = 16; off >= LG; off /= 2) out[m] += __shfl_xor_sync(0xffffffffu, out[m], off);  // the groups
+                    }
+                    if (i < N && grp == 0) {
+                        // One partial per range: the first segment stores, the later ones add to what this lane
+                        // stored before (a handful of fp32 additions of segment sums; the long sums stay inside
+                        // the segments, and the ranges are added in fp64 afterwards).
+                        float* dst = p.partial + (static_cast<size_t>(r) * N + i) * p.Bpad + 4 * q;
+    #pragma unroll
+                        for (int h = 0; h < VPL / 4; ++h) {
+                            if (seg > 0) {
+                                const float4 a = *reinterpret_cast<const float4*>(dst + h * (BT / 2));
+                                out[4 * h] += a.x, out[4 * h + 1] += a.y, out[4 * h + 2] += a.z, out[4 * h + 3] += a.w;
+                            }
+                            *reinterpret_cast<float4*>(dst + h * (BT / 2)) =
+                                make_float4(out[4 * h], out[4 * h + 1], out[4 * h + 2], out[4 * h + 3]);
+                        }
+                    }
                 }
             }
             tmem_wait_store();
@@ -840,7 +978,7 @@ __global__ void __launch_bounds__(THREADS, 1)
             if (i < N && grp == 0) {
                 float* dst = p.partial + (static_cast<size_t>(r) * N + i) * p.Bpad + 4 * q;
                 *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
-                *reinterpret_cast<float4*>(dst + BT / 2) = make_float4(0.f, 0.f, 0.f, 0.f);
+                if constexpr (VPL == 8) *reinterpret_cast<float4*>(dst + BT / 2) = make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
     }
@@ -856,6 +994,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 struct FusedConfig {
     int bpl, ni, iparts, Bpad, R, entCap, segChunks, S;
     int groups;  // lane groups per warp of the group kernel (2: batch 65..128, 4: batch <= 64), 0: ffi_bwd_fused_kernel
+    int vpl;     // batch elements per lane of the group kernel: 8, or 4 for a batch of at most 32
     size_t smem;
 };
 
@@ -867,9 +1006,11 @@ bool fused_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, FusedC
     // the group kernel's entry code holds the position within the chunk in 14 bits
     const bool group_kernel = static_cast<long long>(plan->chunk_rows) * plan->K <= (1 << (32 - kKShift));
     c->groups = group_kernel ? (B > 64 ? 2 : 4) : 0;
+    c->vpl = group_kernel && B <= 32 ? 4 : 8;
     c->bpl = group_kernel ? (B > 64 ? 4 : 2) : (B <= 32 ? 1 : (B <= 64 ? 2 : 4));
-    c->ni = group_kernel ? kGroupNI : 32 / c->bpl;  // ffi_bwd_fused_kernel: 32 accumulator + 32 x registers per lane
-    const int BT = 32 * c->bpl;
+    // ffi_bwd_fused_kernel: 32 accumulator + 32 x registers per lane; the group kernel: 512 TMEM columns per lane quarter
+    c->ni = group_kernel ? (c->vpl == 4 ? 2 * kGroupNI : kGroupNI) : 32 / c->bpl;
+    const int BT = group_kernel ? c->vpl * (32 / c->groups) : 32 * c->bpl;
     const int width = kWarps * c->ni;  // inputs per slice: 128, 256 or 512
     c->iparts = static_cast<int>(ceil_div(plan->N, width));
     c->Bpad = BT;
@@ -911,7 +1052,7 @@ int encode_g_map(CUtensorMap* map, const float* gT, int64_t L, int64_t ldg, int 
         if (q != cudaDriverEntryPointSuccess || !fn) return fail(FFI_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
         encode = reinterpret_cast<EncodeFn>(fn);
     }
-    if (reinterpret_cast<uintptr_t>(gT) % 16 != 0 || chunk_rows > 256 || (BT != 64 && BT != 128))
+    if (reinterpret_cast<uintptr_t>(gT) % 16 != 0 || chunk_rows > 256 || (BT != 32 && BT != 64 && BT != 128))
         return fail(FFI_ERR_INVALID_ARGUMENT, "transposed gradient must be 16-byte aligned, chunks at most 256 rows");
     // the stored rows may be narrower than the tile (batch <= 32 keeps 32 columns): the box's columns past them
     // are filled with zeros, like its rows past L
@@ -1025,6 +1166,8 @@ int launch_backward_fused(const GradXArgs& a, const void* xT, int64_t ldx, float
         };
         if (c.groups == 2 && !a.w_bf16) rc = launch_group(ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 16, 2, float>);
         else if (c.groups == 2) rc = launch_group(ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 16, 2, __nv_bfloat16>);
+        else if (c.vpl == 4 && !a.w_bf16) rc = launch_group(ffi_bwd_pairs_kernel<2 * kGroupNI, kGroupThreads, 8, 4, float, 4>);
+        else if (c.vpl == 4) rc = launch_group(ffi_bwd_pairs_kernel<2 * kGroupNI, kGroupThreads, 8, 4, __nv_bfloat16, 4>);
         else if (!a.w_bf16) rc = launch_group(ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 8, 4, float>);
         else rc = launch_group(ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 8, 4, __nv_bfloat16>);
         if (rc != FFI_OK) return rc;
