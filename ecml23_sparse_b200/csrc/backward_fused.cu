@@ -595,10 +595,13 @@ struct LaneOf<4> {
     using type = Lane4;
 };
 
-// G lane groups per warp: a group of 32/G lanes covers the BT = 256/G batch columns of one entry (8 per lane),
-// so a warp step works on G consecutive entries of a run.  G = 2 is the batch 65..128 case described above;
-// G = 4 covers batch <= 64 with a quarter of a warp per entry (a quarter warp reads one 128-byte half of a
-// tile row per LDS.128: conflict-free), which halves the shared-memory traffic per entry once more.
+// G lane groups per warp and VPL batch elements per lane: a group of 32/G lanes covers the BT = VPL*32/G batch
+// columns of one entry, so a warp step works on G consecutive entries of a run.
+//   batch 65..128: G = 2, VPL = 8 (the case described above; two 16-byte pieces of a tile row per lane);
+//   batch 33..64:  G = 2, VPL = 4 (one 16-byte piece per lane, the tile is [T][64]);
+//   batch <= 32:   G = 4, VPL = 4 (a quarter warp per entry, the tile is [T][32]).
+// With VPL = 4 an input's state is 8 TMEM columns instead of 16, so a warp owns 16 inputs, a CTA 256, and three
+// slices per range instead of six fetch each g tile.
 //
 // TX is the storage type of x and W.  bf16 x is widened (exactly) on its way into tensor memory.  A bf16
 // weight is fetched as the aligned 4-byte word that holds it (cp.async copies at least 4 bytes) and turned
@@ -606,9 +609,6 @@ struct LaneOf<4> {
 // which half: the chunk's first position is even, so the parity of the position within the chunk is the
 // parity of the flat position).
 //
-// VPL = batch elements per lane: 8, or 4 for a batch of at most 32 (G = 4: eight lanes x 4 cover the 32 columns of
-// the tile with ONE 16-byte piece per lane; an input's state is 8 TMEM columns, so a warp owns 16 inputs, a CTA
-// 256, and three slices instead of six fetch each g tile).
 template <int NI, int THREADS, int SLOTS, int G, typename TX, int VPL = 8>
 __global__ void __launch_bounds__(THREADS, 1)
     ffi_bwd_pairs_kernel(BwdFusedParams p, const __grid_constant__ CUtensorMap g_map) {
@@ -993,8 +993,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 
 struct FusedConfig {
     int bpl, ni, iparts, Bpad, R, entCap, segChunks, S;
-    int groups;  // lane groups per warp of the group kernel (2: batch 65..128, 4: batch <= 64), 0: ffi_bwd_fused_kernel
-    int vpl;     // batch elements per lane of the group kernel: 8, or 4 for a batch of at most 32
+    int groups;  // lane groups per warp of the group kernel (2: batch 33..128, 4: batch <= 32), 0: ffi_bwd_fused_kernel
+    int vpl;     // batch elements per lane of the group kernel: 8 (batch 65..128) or 4
     size_t smem;
 };
 
@@ -1005,8 +1005,8 @@ bool fused_config(const ffi_plan* plan, int64_t B, const DeviceInfo& dev, FusedC
     if (plan->K >= (1 << (32 - kKShift))) return false;  // k shares the entry's code word with the row offset
     // the group kernel's entry code holds the position within the chunk in 14 bits
     const bool group_kernel = static_cast<long long>(plan->chunk_rows) * plan->K <= (1 << (32 - kKShift));
-    c->groups = group_kernel ? (B > 64 ? 2 : 4) : 0;
-    c->vpl = group_kernel && B <= 32 ? 4 : 8;
+    c->groups = group_kernel ? (B > 32 ? 2 : 4) : 0;
+    c->vpl = group_kernel && B <= 64 ? 4 : 8;
     c->bpl = group_kernel ? (B > 64 ? 4 : 2) : (B <= 32 ? 1 : (B <= 64 ? 2 : 4));
     // ffi_bwd_fused_kernel: 32 accumulator + 32 x registers per lane; the group kernel: 512 TMEM columns per lane quarter
     c->ni = group_kernel ? (c->vpl == 4 ? 2 * kGroupNI : kGroupNI) : 32 / c->bpl;
@@ -1164,12 +1164,12 @@ int launch_backward_fused(const GradXArgs& a, const void* xT, int64_t ldx, float
             kern<<<grid, kGroupThreads, c.smem, stream>>>(p, g_map);
             return FFI_OK;
         };
-        if (c.groups == 2 && !a.w_bf16) rc = launch_group(ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 16, 2, float>);
-        else if (c.groups == 2) rc = launch_group(ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 16, 2, __nv_bfloat16>);
-        else if (c.vpl == 4 && !a.w_bf16) rc = launch_group(ffi_bwd_pairs_kernel<2 * kGroupNI, kGroupThreads, 8, 4, float, 4>);
-        else if (c.vpl == 4) rc = launch_group(ffi_bwd_pairs_kernel<2 * kGroupNI, kGroupThreads, 8, 4, __nv_bfloat16, 4>);
-        else if (!a.w_bf16) rc = launch_group(ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 8, 4, float>);
-        else rc = launch_group(ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 8, 4, __nv_bfloat16>);
+        if (c.groups == 2 && c.vpl == 8 && !a.w_bf16) rc = launch_group(ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 16, 2, float>);
+        else if (c.groups == 2 && c.vpl == 8) rc = launch_group(ffi_bwd_pairs_kernel<kGroupNI, kGroupThreads, 16, 2, __nv_bfloat16>);
+        else if (c.groups == 2 && c.vpl == 4 && !a.w_bf16) rc = launch_group(ffi_bwd_pairs_kernel<2 * kGroupNI, kGroupThreads, 16, 2, float, 4>);
+        else if (c.groups == 2 && c.vpl == 4) rc = launch_group(ffi_bwd_pairs_kernel<2 * kGroupNI, kGroupThreads, 16, 2, __nv_bfloat16, 4>);
+        else if (!a.w_bf16) rc = launch_group(ffi_bwd_pairs_kernel<2 * kGroupNI, kGroupThreads, 8, 4, float, 4>);
+        else rc = launch_group(ffi_bwd_pairs_kernel<2 * kGroupNI, kGroupThreads, 8, 4, __nv_bfloat16, 4>);
         if (rc != FFI_OK) return rc;
         FFI_LAUNCH_CHECK("ffi_bwd_pairs_kernel");
         rc = FFI_OK;
