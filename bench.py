@@ -609,14 +609,28 @@ def run_ours(args):
     # ---- end to end from host buffers -----------------------------------------------------
     e2e = None
     if not args.no_e2e:
-        x_host = synth.normal(SEED, 0, (N, B)).t().contiguous().to(store_dtype).pin_memory()  # [B,N] on the host
-        rp_host, lab_host = synth.multi_hot_targets(SEED, 5, B, L)
-        rp_host, lab_host = rp_host.pin_memory(), lab_host.pin_memory()
-        x_dev = torch.empty((B, N), dtype=store_dtype, device=dev)
-        rp_dev = torch.empty_like(rp_host, device=dev)
-        lab_dev = torch.empty_like(lab_host, device=dev)
-        gx_host = torch.empty((B, N)).pin_memory()
-        loss_host = torch.empty(()).pin_memory()
+        # The step's inputs (x [B,N], CSR targets) sit in ONE pinned staging buffer and cross PCIe as one copy;
+        # grad_x and the loss come back the same way (they already share a device buffer).
+        x_src = synth.normal(SEED, 0, (N, B)).t().contiguous().to(store_dtype)  # [B,N] on the host
+        rp_src, lab_src = synth.multi_hot_targets(SEED, 5, B, L)
+
+        def aligned(nbytes):
+            return -(-nbytes // 256) * 256
+
+        sizes = [t.numel() * t.element_size() for t in (x_src, rp_src, lab_src)]
+        offs = [0, aligned(sizes[0]), aligned(sizes[0]) + aligned(sizes[1])]
+        in_bytes = offs[2] + sizes[2]
+        in_host = torch.empty(in_bytes, dtype=torch.uint8).pin_memory()
+        in_dev = torch.empty(in_bytes, dtype=torch.uint8, device=dev)
+
+        def views(base):
+            return [base[o:o + n].view(t.dtype).view(t.shape) for o, n, t in zip(offs, sizes, (x_src, rp_src, lab_src))]
+
+        x_host, rp_host, lab_host = views(in_host)
+        x_host.copy_(x_src), rp_host.copy_(rp_src), lab_host.copy_(lab_src)
+        x_dev, rp_dev, lab_dev = views(in_dev)
+        out_host = torch.empty(N * B + 1).pin_memory()
+        gx_host, loss_host = out_host[:N * B].view(B, N), out_host[N * B]
 
         # grad_x and the loss travel together: one buffer of N*B + 4 floats per rank (a slot of the symmetric
         # allocation where there is one), one exchange per step
@@ -632,9 +646,7 @@ def run_ours(args):
 
         def compute_e2e():
             """Host -> device copies and this rank's kernels; leaves (grad_x partial, loss share) in the buffer."""
-            x_dev.copy_(x_host, non_blocking=True)
-            rp_dev.copy_(rp_host, non_blocking=True)
-            lab_dev.copy_(lab_host, non_blocking=True)
+            in_dev.copy_(in_host, non_blocking=True)
             # logits never reach HBM: the forward kernel's epilogue writes the BCE gradient, transposed
             loss, gT = ops.forward_bce(x_dev, idx, W, bias, rp_dev, lab_dev, False, total_labels=L, label_offset=lo)
             buf = e2e_buffer()
@@ -652,8 +664,7 @@ def run_ours(args):
             elif e2e_mode == "nccl":
                 dist.all_reduce(buf)
             gx, loss = buf[:N * B].view(B, N), buf[N * B]
-            gx_host.copy_(gx, non_blocking=True)
-            loss_host.copy_(loss, non_blocking=True)
+            out_host.copy_(buf[:N * B + 1], non_blocking=True)
             return gx, loss
 
         def step_e2e_eager():
@@ -690,7 +701,7 @@ def run_ours(args):
 
         def e2e_partials():
             """This rank's grad_x partial and loss share of the same step, without any exchange."""
-            x_dev.copy_(x_host)
+            in_dev.copy_(in_host)
             loss, gT = ops.forward_bce(x_dev, idx, W, bias, rp_dev, lab_dev, False, total_labels=L, label_offset=lo)
             gx = ops._backward(x_dev, idx, W, gT, False, plan=plan, grad_is_transposed=True)[0]
             return [gx, loss.view(1)]
@@ -703,11 +714,12 @@ def run_ours(args):
         (e2e_ms, _, _), e2e_reps = median_loop(step_e2e)
         e2e = {
             "value": B / (e2e_ms / args.steps * 1e-3), "unit": "samples/s",
-            "h2d_bytes_per_step": int(x_host.numel() * esize + rp_host.numel() * 4 + lab_host.numel() * 4),
-            "d2h_bytes_per_step": int(gx_host.numel() * 4 + 4),
+            "h2d_bytes_per_step": int(in_bytes),
+            "d2h_bytes_per_step": int(out_host.numel() * 4),
             "ms_per_step": e2e_ms / args.steps, "ms_per_step_reps": e2e_reps,
-            "path": "pinned host x[B,N] + CSR targets -> FanInSparseMatmul(+bias) with fused sigmoid-BCE gradient -> "
-                    "FanInSparseMatmulGrad (grad_x, grad_W, grad_bias) -> loss and grad_x to host",
+            "path": "pinned host x[B,N] + CSR targets (one staging buffer, one copy) -> FanInSparseMatmul(+bias) with fused "
+                    "sigmoid-BCE gradient -> FanInSparseMatmulGrad (grad_x, grad_W, grad_bias) -> grad_x and loss to host "
+                    "(one copy)",
             "launch": "copies in and the rank's kernels replayed as one CUDA graph, then exchange and copies out"
                       if e2e_graph is not None else "call by call",
         }
