@@ -611,7 +611,7 @@ def run_ours(args):
     if not args.no_e2e:
         # The step's inputs (x [B,N], CSR targets) sit in ONE pinned staging buffer and cross PCIe as one copy;
         # grad_x and the loss come back the same way (they already share a device buffer).
-        x_src = synth.normal(SEED, 0, (N, B)).t().contiguous().to(store_dtype)  # [B,N] on the host
+        x_src = synth.normal(SEED, 0, (N, B)).to(store_dtype)  # [N,B] on the host: the transposed op, as the resident leg
         rp_src, lab_src = synth.multi_hot_targets(SEED, 5, B, L)
 
         def aligned(nbytes):
@@ -630,7 +630,7 @@ def run_ours(args):
         x_host.copy_(x_src), rp_host.copy_(rp_src), lab_host.copy_(lab_src)
         x_dev, rp_dev, lab_dev = views(in_dev)
         out_host = torch.empty(N * B + 1).pin_memory()
-        gx_host, loss_host = out_host[:N * B].view(B, N), out_host[N * B]
+        gx_host, loss_host = out_host[:N * B].view(N, B), out_host[N * B]
 
         # grad_x and the loss travel together: one buffer of N*B + 4 floats per rank (a slot of the symmetric
         # allocation where there is one), one exchange per step
@@ -648,10 +648,10 @@ def run_ours(args):
             """Host -> device copies and this rank's kernels; leaves (grad_x partial, loss share) in the buffer."""
             in_dev.copy_(in_host, non_blocking=True)
             # logits never reach HBM: the forward kernel's epilogue writes the BCE gradient, transposed
-            loss, gT = ops.forward_bce(x_dev, idx, W, bias, rp_dev, lab_dev, False, total_labels=L, label_offset=lo)
+            loss, gT = ops.forward_bce(x_dev, idx, W, bias, rp_dev, lab_dev, True, total_labels=L, label_offset=lo)
             buf = e2e_buffer()
             buf[N * B:N * B + 1].copy_(loss.view(1))
-            ops._backward(x_dev, idx, W, gT, False, plan=plan, want_bias_grad=True, grad_is_transposed=True,
+            ops._backward(x_dev, idx, W, gT, True, plan=plan, want_bias_grad=True, grad_is_transposed=True,
                           feature_grad_out=buf[:N * B])
             return buf
 
@@ -663,7 +663,7 @@ def run_ours(args):
                 buf = peer.sum(peer_out)
             elif e2e_mode == "nccl":
                 dist.all_reduce(buf)
-            gx, loss = buf[:N * B].view(B, N), buf[N * B]
+            gx, loss = buf[:N * B].view(N, B), buf[N * B]
             out_host.copy_(buf[:N * B + 1], non_blocking=True)
             return gx, loss
 
@@ -702,8 +702,8 @@ def run_ours(args):
         def e2e_partials():
             """This rank's grad_x partial and loss share of the same step, without any exchange."""
             in_dev.copy_(in_host)
-            loss, gT = ops.forward_bce(x_dev, idx, W, bias, rp_dev, lab_dev, False, total_labels=L, label_offset=lo)
-            gx = ops._backward(x_dev, idx, W, gT, False, plan=plan, grad_is_transposed=True)[0]
+            loss, gT = ops.forward_bce(x_dev, idx, W, bias, rp_dev, lab_dev, True, total_labels=L, label_offset=lo)
+            gx = ops._backward(x_dev, idx, W, gT, True, plan=plan, grad_is_transposed=True)[0]
             return [gx, loss.view(1)]
 
         if world > 1:
@@ -717,8 +717,8 @@ def run_ours(args):
             "h2d_bytes_per_step": int(in_bytes),
             "d2h_bytes_per_step": int(out_host.numel() * 4),
             "ms_per_step": e2e_ms / args.steps, "ms_per_step_reps": e2e_reps,
-            "path": "pinned host x[B,N] + CSR targets (one staging buffer, one copy) -> FanInSparseMatmul(+bias) with fused "
-                    "sigmoid-BCE gradient -> FanInSparseMatmulGrad (grad_x, grad_W, grad_bias) -> grad_x and loss to host "
+            "path": "pinned host x[N,B] + CSR targets (one staging buffer, one copy) -> FanInSparseMatmulTp(+bias) with fused "
+                    "sigmoid-BCE gradient -> FanInSparseMatmulGradTp (grad_x, grad_W, grad_bias) -> grad_x and loss to host "
                     "(one copy)",
             "launch": "copies in and the rank's kernels replayed as one CUDA graph, then exchange and copies out"
                       if e2e_graph is not None else "call by call",
