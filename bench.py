@@ -648,9 +648,9 @@ def run_ours(args):
             """Host -> device copies and this rank's kernels; leaves (grad_x partial, loss share) in the buffer."""
             in_dev.copy_(in_host, non_blocking=True)
             # logits never reach HBM: the forward kernel's epilogue writes the BCE gradient, transposed
-            loss, gT = ops.forward_bce(x_dev, idx, W, bias, rp_dev, lab_dev, True, total_labels=L, label_offset=lo)
             buf = e2e_buffer()
-            buf[N * B:N * B + 1].copy_(loss.view(1))
+            _, gT = ops.forward_bce(x_dev, idx, W, bias, rp_dev, lab_dev, True, total_labels=L, label_offset=lo,
+                                    loss_out=buf[N * B:N * B + 1])
             ops._backward(x_dev, idx, W, gT, True, plan=plan, want_bias_grad=True, grad_is_transposed=True,
                           feature_grad_out=buf[:N * B])
             return buf

@@ -252,13 +252,13 @@ def _backward(features, lookup, weights, out_grad, transposed: bool, plan: Optio
 
 
 def forward_bce(features, lookup, weights, bias, row_ptr, labels, transposed: bool, total_labels=None,
-                label_offset: int = 0, loss: str = "bce"):
+                label_offset: int = 0, loss: str = "bce", loss_out=None):
     """Forward with the loss gradient fused into its epilogue: returns (loss scalar tensor, gT[L][ldg]).
     `loss` is "bce" (SparseBinaryCrossEntropyLoss), "squared_hinge" (SparseSquaredHingeLoss, the
     one the reference's task files select) or "hinge" (SparseHingeLoss); sparse/metrics.py:132-173.
 
-    The logits are never materialised.  Raises FFIError (FFI_ERR_UNSUPPORTED) for shapes the fused
-    kernel does not cover; use `_forward` + `sparse_bce_with_logits` there."""
+    The logits are never materialised.  `loss_out` (optional, one fp32 element on the device) receives the
+    loss scalar in place, e.g. a slot of the buffer a label-sharded step exchanges."""
     features = _check_cuda("features", features, _STORAGE_DTYPES)
     weights = _check_cuda("weights", weights, _STORAGE_DTYPES)
     dtype = _storage_dtype(features, weights)
@@ -272,7 +272,10 @@ def forward_bce(features, lookup, weights, bias, row_ptr, labels, transposed: bo
         raise ValueError("row_ptr must have B+1 entries")
     ldg = int(lib.ffi_transposed_gradient_stride(B))
     gT = torch.empty((L, ldg), dtype=torch.float32, device=dev)
-    loss_out = torch.empty((), dtype=torch.float32, device=dev)
+    if loss_out is None:
+        loss_out = torch.empty((), dtype=torch.float32, device=dev)
+    elif loss_out.dtype != torch.float32 or loss_out.numel() != 1 or loss_out.device != dev:
+        raise ValueError("loss_out must be one fp32 element on the features' device")
     with torch.cuda.device(dev):
         ws_bytes = lib.ffi_forward_bce_workspace_bytes(B, N, L, K, int(transposed), dtype)
         ws = _workspace(dev, ws_bytes + 256)
